@@ -25,7 +25,8 @@ window: the next query, at position `length`, sees keys from `length - window + 
 pages that lie wholly before that are returned when the length is published and their
 table entries are cleared.  Work already put on the stream may still read them; whoever
 takes them next writes them in work that is put on the stream later.  Such a sequence
-holds about `window / 64 + 2` pages however long it grows.
+holds about `window / 64 + 2` pages however long it grows.  A need with a `chunk` does the
+same with the pages that lie wholly before the chunk of the next position.
 """
 from __future__ import annotations
 
@@ -84,7 +85,15 @@ class _KVGroup:
         self.released: Dict[int, int] = {}            # how many older pages it has given back already (a window's doing)
 
     def tokens_read(self, length: int) -> int:
+        if self.need.chunk:
+            return length - length // self.need.chunk * self.need.chunk
         return min(length, self.need.window) if self.need.window else length
+
+    def first_kept(self, length: int) -> int:
+        """The oldest position that a query at position `length` (the next one) can still read."""
+        if self.need.chunk:
+            return length // self.need.chunk * self.need.chunk
+        return max(0, length - self.need.window + 1) if self.need.window else 0
 
     def bytes_per_token(self) -> int:
         if self.need.kind == "rows":
@@ -114,8 +123,8 @@ class SequenceCache:
         # A sequence cannot hold more pages than there are, unless every kv group lets old pages go (a window) or the model
         # keeps no keys and values at all (state of fixed size only).
         kv_needs = [need for need, _ in groups.values() if need.kind in ("kv", "rows")]
-        bounded = all(need.window for need in kv_needs)
-        self.widest_window = max((need.window for need in kv_needs), default=0) if bounded else None
+        bounded = all(need.window or need.chunk for need in kv_needs)
+        self.widest_window = max((need.window or need.chunk for need in kv_needs), default=0) if bounded else None
         # ... but its page table is addressed by position, so a sequence is given at most 64 times the pages of the whole cache
         # (1,024 at least), not the 2^31 positions that a design without a position limit would allow.
         self.pages_per_sequence = (min(pages_for(max_sequence_tokens), max(64 * self.n_pages, 1024)) if bounded
@@ -186,10 +195,10 @@ class SequenceCache:
             raise ValueError("a sequence cannot shrink")
         self.lengths[slot] = new_length
         for group in self.kv.values():
-            if not group.need.window:
+            if not (group.need.window or group.need.chunk):
                 continue
-            # The next query sits at position `new_length` and sees keys from `new_length - window + 1` on.
-            keep_from = max(0, new_length - group.need.window + 1) // PAGE_TOKENS
+            # The next query sits at position `new_length` and sees keys from `new_length - window + 1` (or its chunk's first) on.
+            keep_from = group.first_kept(new_length) // PAGE_TOKENS
             gone = keep_from - group.released[slot]
             if gone > 0:
                 held = group.held[slot]
@@ -241,7 +250,7 @@ class SequenceCache:
             for slot, pages in group.held.items():
                 if self.lengths[slot] > (group.released[slot] + len(pages)) * PAGE_TOKENS:
                     raise AssertionError("a sequence is longer than the pages it holds")
-                if group.released[slot] and not group.need.window:
+                if group.released[slot] and not (group.need.window or group.need.chunk):
                     raise AssertionError("a group without a window gave pages back early")
-                if group.need.window and group.released[slot] * PAGE_TOKENS > max(0, self.lengths[slot] - group.need.window + 1):
+                if group.released[slot] * PAGE_TOKENS > group.first_kept(self.lengths[slot]):
                     raise AssertionError("a page inside the window was given back")

@@ -6,5 +6,7 @@ from .registry import (Architecture, architecture_for, register_architecture, re
                        spec_from_config_json, unregister_architecture)
 from .fasesun import FasesunConfig
 from .bisudra import BisudraConfig
-from .specs import (AttentionSpec, BlockSpec, DenseFeedForwardSpec, DifferentialAttentionSpec, LatentAttentionSpec, LinearRecurrenceSpec, ModelSpec, NormSpec, PairRotationSpec,
+from .pegurax import PeguraxConfig
+from .specs import (AttentionSpec, BlockSpec, DeltaRuleSpec, DenseFeedForwardSpec, DifferentialAttentionSpec, MaskedAttentionSpec, SandwichBlockSpec,
+                    ScaledRotationSpec, SelectiveScanSpec, SideBySideSpec, LatentAttentionSpec, LinearRecurrenceSpec, ModelSpec, NormSpec, PairRotationSpec,
                     PositionSpec, RoutedExpertsSpec, ScheduleEntry, SublayerNormBlockSpec, SwiGLUSpec, TokenSideSpec)

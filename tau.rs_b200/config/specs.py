@@ -22,6 +22,7 @@ class NormSpec:
     eps: float
     kind: str = "rms_norm"
     bias_suffix: str = ".bias"
+    bias: bool = True          # a layer norm without a bias has no such tensor
 
 
 @dataclass(frozen=True)
@@ -50,7 +51,7 @@ class AttentionSpec:
 
 @dataclass(frozen=True)
 class SwiGLUSpec:
-    """`down(silu(gate(x)) * up(x))`.  The three tensors are `<prefix>.<name><weight_suffix>`."""
+    """`down(act(gate(x)) * up(x))` with `act` = `activation` ("silu" or "relu").  The three tensors are `<prefix>.<name><weight_suffix>`."""
 
     hidden: int
     intermediate: int
@@ -59,6 +60,7 @@ class SwiGLUSpec:
     up_name: str = "up_proj"
     down_name: str = "down_proj"
     weight_suffix: str = ".weight"
+    activation: str = "silu"
 
 
 @dataclass(frozen=True)
@@ -170,11 +172,99 @@ class LinearRecurrenceSpec:
 
 
 @dataclass(frozen=True)
+class ScaledRotationSpec:
+    """Rotary position encoding of the first `rotary_dim` elements of each head in which element `i` is paired with element
+    `i + rotary_dim / 2`; the angle of pair `i` at position `p` is `p * f_i` with `f_i = theta^(-2i / rotary_dim)`.  With `factor`
+    (not None) the frequencies are blended between `f_i` and `f_i / factor` (YaRN): with `index(t) = rotary_dim * ln(original /
+    (2 pi t)) / (2 ln theta)`, `lo = max(floor(index(fast)), 0)`, `hi = min(ceil(index(slow)), rotary_dim - 1)` and `ramp_i =
+    clamp((i - lo) / max(hi - lo, 0.001), 0, 1)` the frequency is `f_i / factor * ramp_i + f_i * (1 - ramp_i)`, and sine and cosine
+    are multiplied by `0.1 ln(factor) + 1`."""
+
+    rotary_dim: int
+    theta: float
+    factor: Optional[float] = None
+    original: float = 0.0
+    fast: float = 0.0
+    slow: float = 0.0
+    kind: str = "rope_half_scaled"
+
+
+@dataclass(frozen=True)
+class MaskedAttentionSpec:
+    """Grouped-query softmax attention whose keys (`dim`) and values (`value_dim`) may differ in size, over one cached row per
+    position.  `qk_norm == "projection"`: queries, and keys, pass an RMS norm over their whole projection (all heads at once) with a
+    weight of that size, before `position`.  A query at position i sees key j <= i within `window` positions, or (with `chunk`)
+    only if floor(j / chunk) == floor(i / chunk), chunks counted from position 0.  `sink`: one is added to the softmax's
+    denominator (a key with score 0 and no value).  `out_scale` multiplies what the output projection reads."""
+
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    dim: int
+    value_dim: int
+    softmax_scale: float
+    eps: float = 1e-6
+    qk_norm: Optional[str] = None
+    position: Optional[ScaledRotationSpec] = None
+    window: Optional[int] = None
+    chunk: Optional[int] = None
+    sink: bool = False
+    kind: str = "masked_attention"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """The gated delta rule: per head a matrix state `S` (`key_dim` x `value_dim`), `S <- g S; u = beta (v - S^T k); S <- S + k
+    u^T; o = S^T q`.  Queries and keys belong to `n_key_heads` heads (value head h reads key head h / (n_heads / n_key_heads)).
+    q, k and v each pass a causal convolution of `taps` taps per channel and SiLU; q and k are then unit vectors per head, q times
+    `key_dim^-1/2`; `beta = sigmoid(W_b h)`; `g = exp(-exp(A_log) softplus(W_a h + dt_bias))`.  Each head's read-out is divided by
+    its root mean square (`eps`), times a weight of `value_dim` elements shared by the heads, times `silu(W_g h)`."""
+
+    hidden: int
+    n_heads: int
+    n_key_heads: int
+    key_dim: int
+    value_dim: int
+    taps: int
+    eps: float
+    kind: str = "gated_delta_rule"
+
+
+@dataclass(frozen=True)
+class SelectiveScanSpec:
+    """A Mamba mixer: `[x | z] = W_in h`; x passes a causal convolution of `taps` taps per channel (with bias) and SiLU;
+    `[dt | B | C] = W_x x` (`dt_rank`, `states`, `states`); `step = softplus(W_dt dt + b_dt)`; per channel and state
+    `S <- exp(step A) S + step x B`, `y = S . C + D x` with `A = -exp(A_log)`; the output is `W_o (y silu(z))`."""
+
+    hidden: int
+    inner: int
+    states: int
+    dt_rank: int
+    taps: int
+    kind: str = "selective_scan"
+
+
+@dataclass(frozen=True)
+class SideBySideSpec:
+    """Two mixers that read the same input; the result is `left_scale * left(h) + right_scale * right(h)`.  Their tensors lie under
+    `<prefix>.<left_name>` and `<prefix>.<right_name>`."""
+
+    left: object
+    right: object
+    left_scale: float = 1.0
+    right_scale: float = 1.0
+    left_name: str = "left"
+    right_name: str = "right"
+    kind: str = "side_by_side"
+
+
+@dataclass(frozen=True)
 class RoutedExpertsSpec:
     """`top` of `experts` gated feed-forwards per token.  The router's logits pass through `score` ("sigmoid" or
     "softmax"); experts are chosen by score plus a correction per expert (if `correction`), weighted by the score itself,
     renormalised over the chosen ones only if `renormalize` (a softmax score renormalised is the softmax over the chosen logits
-    alone).  `router_bias` adds the tensor `<prefix>.router.b` to the logits.  `shared` is a feed-forward that every token passes; with
+    alone).  `router_bias` adds the tensor `<prefix>.router.b` to the logits.  `weigh` says what an expert's weight multiplies:
+    its `"output"`, or its `"input"` (the expert then reads `weight * h`).  `shared` is a feed-forward that every token passes; with
     `shared_gate` its output is scaled by the sigmoid of one more projection of the token."""
 
     hidden: int
@@ -188,6 +278,7 @@ class RoutedExpertsSpec:
     shared_gate: bool = False
     kind: str = "routed_experts"
     router_bias: bool = False
+    weigh: str = "output"
 
 
 @dataclass(frozen=True)
@@ -223,6 +314,23 @@ class SublayerNormBlockSpec:
     token_side: Optional[TokenSideSpec] = None
     depth_mix: int = 0
     kind: str = "sublayer_norm"
+
+
+@dataclass(frozen=True)
+class SandwichBlockSpec:
+    """One layer with a norm before and behind each sublayer, on a residual stream kept in 32-bit:
+    `x <- x + s1 * post1(mixer(pre1(x)))`, then `x <- x + s2 * post2(feed_forward(pre2(x)))` (absent without a feed-forward).
+    With `layer_scale` the vectors `s1`, `s2` (`<prefix>.<scale names>`) multiply the normalised results element by element."""
+
+    prefix: str
+    mixer: object
+    feed_forward: object
+    mixer_norm: NormSpec
+    mixer_post_norm: NormSpec
+    feed_forward_norm: Optional[NormSpec]
+    feed_forward_post_norm: Optional[NormSpec]
+    layer_scale: bool = True
+    kind: str = "sandwich"
 
 
 @dataclass(frozen=True)
@@ -270,3 +378,6 @@ class ModelSpec:
     # Tensors that belong to no single block: (name, shape, role).  The model reads them and hands each to the blocks that
     # list its name in `shared_tensor_names()`.
     shared_tensors: Tuple[Tuple[str, Tuple[int, ...], str], ...] = ()
+    # The embedded rows are multiplied by this as they enter the residual stream (a 32-bit stream if it is not 1); the head reads
+    # the table as it is.
+    embedding_scale: float = 1.0

@@ -1,0 +1,166 @@
+// The gated delta rule: a matrix state S (key_dim x value_dim) per head that decays, is corrected towards the token's value along
+// the token's key, and is read with the token's query:
+//
+//     S <- g S;   u = beta (v - S^T k);   S <- S + k u^T;   o = S^T q            (the read-out sees the token's own write)
+//
+// `q` and `k` belong to key heads (value head h reads key head h / (heads / key_heads)); q and k are unit vectors per head
+// (x / sqrt(sum x^2 + 1e-6)), q also times key_dim^-1/2; beta = sigmoid(b); g = exp(-exp(A_log) softplus(a + dt_bias)).
+//
+//   prepare:  per token, in 32-bit and in place on [q | k | v] rows: the two unit norms and the query's scale, k . q per key head,
+//             and (g, beta) per value head from the pre-activations.
+//   walk:     one block owns (sequence, head, tile of value columns) and walks the run's tokens in order.  A column of S is shared by
+//             kSplit threads, each with kRows key rows in registers.  With a = S_old^T k and b = S_old^T q (both from the state
+//             before the token, one pass and one barrier) the token's result is u = beta (v - g a), o = g b + u (k . q),
+//             S = g S_old + k u^T: the equations above with the decay pulled out of the sums.
+//
+// The state is 32-bit and lives in the cache, [heads, value_dim, key_dim] per slot.  TAU_KEY_DIM fixes key_dim.
+#include "common.cuh"
+
+#ifndef TAU_KEY_DIM
+#error "compile with -DTAU_KEY_DIM=<key elements per head>"
+#endif
+
+namespace {
+
+constexpr int kDim = TAU_KEY_DIM;
+constexpr int kSplit = kDim <= 16 ? 1 : kDim <= 32 ? 2 : kDim <= 64 ? 4 : kDim <= 128 ? 8 : kDim <= 256 ? 16 : 32;   // threads that share a column
+constexpr int kRows = (kDim + kSplit - 1) / kSplit;
+
+// grid: tokens; block: 128.  rows [tokens, stride] float: q at q_offset (key_heads * kDim), k at k_offset.  pre [tokens, 2 heads]:
+// the pre-activations of beta, then of the decay's step.  gates [tokens, heads, 2] = (g, beta); kq [tokens, key_heads].
+__global__ void __launch_bounds__(128)
+delta_prepare_kernel(float* __restrict__ rows, long long stride, int q_offset, int k_offset, const float* __restrict__ pre, const float* __restrict__ a_log,
+                     const float* __restrict__ dt_bias, float* __restrict__ gates, float* __restrict__ kq, int heads, int key_heads, float query_scale) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+    float* row = rows + static_cast<size_t>(token) * stride;
+    for (int head = warp; head < key_heads; head += warps) {
+        float* q = row + q_offset + head * kDim;
+        float* k = row + k_offset + head * kDim;
+        float qq = 0.0f, kk = 0.0f;
+        for (int d = lane; d < kDim; d += 32) {
+            qq = fmaf(q[d], q[d], qq);
+            kk = fmaf(k[d], k[d], kk);
+        }
+        const float q_factor = query_scale / sqrtf(warp_sum(qq) + 1e-6f), k_factor = 1.0f / sqrtf(warp_sum(kk) + 1e-6f);
+        float dot = 0.0f;
+        for (int d = lane; d < kDim; d += 32) {
+            const float a = q[d] * q_factor, b = k[d] * k_factor;
+            q[d] = a;
+            k[d] = b;
+            dot = fmaf(a, b, dot);
+        }
+        dot = warp_sum(dot);
+        if (lane == 0) kq[static_cast<size_t>(token) * key_heads + head] = dot;
+    }
+    for (int head = threadIdx.x; head < heads; head += blockDim.x) {
+        const float b = pre[static_cast<size_t>(token) * 2 * heads + head];
+        const float z = pre[static_cast<size_t>(token) * 2 * heads + heads + head] + dt_bias[head];
+        const float soft = z > 20.0f ? z : log1pf(expf(z));
+        gates[(static_cast<size_t>(token) * heads + head) * 2] = expf(-expf(a_log[head]) * soft);
+        gates[(static_cast<size_t>(token) * heads + head) * 2 + 1] = 1.0f / (1.0f + expf(-b));
+    }
+}
+
+template <int kColumns>
+__global__ void __launch_bounds__(kColumns * kSplit)
+delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset, int k_offset, int v_offset, const float* __restrict__ gates,
+                  const float* __restrict__ kq, float* __restrict__ state, long long slot_stride, const int* __restrict__ cu_seqlens,
+                  const int* __restrict__ seq_slot, float* __restrict__ out, int heads, int key_heads, int value_dim) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    __shared__ float qs[2][kDim], ks[2][kDim], part_a[2][kSplit][kColumns], part_b[2][kSplit][kColumns];
+    const int head = blockIdx.x, sequence = blockIdx.y, key_head = head / (heads / key_heads);
+    const int local = threadIdx.x % kColumns, part = threadIdx.x / kColumns, row0 = part * kRows;
+    const int column = blockIdx.z * kColumns + local;
+    const bool live = column < value_dim;
+    float* record = state + static_cast<size_t>(seq_slot[sequence]) * slot_stride + (static_cast<size_t>(head) * value_dim + (live ? column : 0)) * kDim;
+    float S[kRows];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r) S[r] = (live && row0 + r < kDim) ? record[row0 + r] : 0.0f;
+    const int begin = cu_seqlens[sequence], end = cu_seqlens[sequence + 1];
+    constexpr int kStage = (kDim + kColumns * kSplit - 1) / (kColumns * kSplit);
+    auto stage = [&](int token, int half) {      // the token's q and k into one half of shared memory
+        const float* row = rows + static_cast<size_t>(token) * stride;
+#pragma unroll
+        for (int i = 0; i < kStage; ++i) {
+            const int d = threadIdx.x + i * kColumns * kSplit;
+            if (d < kDim) {
+                qs[half][d] = row[q_offset + key_head * kDim + d];
+                ks[half][d] = row[k_offset + key_head * kDim + d];
+            }
+        }
+    };
+    if (begin < end) stage(begin, 0);
+    __syncthreads();
+    for (int token = begin; token < end; ++token) {
+        const int half = (token - begin) & 1;
+        // Asked for before the sums, used behind the barrier.
+        const float value = live ? rows[static_cast<size_t>(token) * stride + v_offset + head * value_dim + column] : 0.0f;
+        const float decay = gates[(static_cast<size_t>(token) * heads + head) * 2], beta = gates[(static_cast<size_t>(token) * heads + head) * 2 + 1];
+        const float key_query = kq[static_cast<size_t>(token) * key_heads + key_head];
+        float key[kRows];
+        float a[2] = {0.0f, 0.0f}, b[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            key[r] = row0 + r < kDim ? ks[half][row0 + r] : 0.0f;
+            const float query = row0 + r < kDim ? qs[half][row0 + r] : 0.0f;
+            a[r & 1] = fmaf(S[r], key[r], a[r & 1]);
+            b[r & 1] = fmaf(S[r], query, b[r & 1]);
+        }
+        part_a[half][part][local] = a[0] + a[1];
+        part_b[half][part][local] = b[0] + b[1];
+        if (token + 1 < end) stage(token + 1, half ^ 1);       // nobody reads that half now: this token's q and k were read above
+        __syncthreads();
+        float sum_a = 0.0f, sum_b = 0.0f;
+#pragma unroll
+        for (int p = 0; p < kSplit; ++p) {
+            sum_a += part_a[half][p][local];
+            sum_b += part_b[half][p][local];
+        }
+        const float update = beta * (value - decay * sum_a);
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) S[r] = fmaf(decay, S[r], key[r] * update);
+        if (part == 0 && live) out[(static_cast<size_t>(token) * heads + head) * value_dim + column] = fmaf(decay, sum_b, update * key_query);
+    }
+    if (live) {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            if (row0 + r < kDim) record[row0 + r] = S[r];
+    }
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_delta_key_dim() { return kDim; }
+
+TAU_EXPORT int tau_delta_prepare(float* rows, long long stride, int q_offset, int k_offset, const float* pre, const float* a_log, const float* dt_bias,
+                                 float* gates, float* kq, int tokens, int heads, int key_heads, float query_scale, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!rows || !pre || !a_log || !dt_bias || !gates || !kq || heads <= 0 || key_heads <= 0 || heads % key_heads != 0) return cudaErrorInvalidValue;
+    tau_launch(delta_prepare_kernel, dim3(tokens), dim3(128), 0, static_cast<cudaStream_t>(stream), rows, stride, q_offset, k_offset, pre, a_log, dt_bias,
+               gates, kq, heads, key_heads, query_scale);
+    return tau_launch_status();
+}
+
+// rows [tokens, stride] float with q, k (key_heads * key_dim each) and v (heads * value_dim) at their offsets, prepared as above.
+// state: [heads, value_dim, key_dim] floats per slot, slots `slot_stride` apart.  out [tokens, heads * value_dim].
+TAU_EXPORT int tau_delta_rule(const float* rows, long long stride, int q_offset, int k_offset, int v_offset, const float* gates, const float* kq,
+                              float* state, long long slot_stride, const int* cu_seqlens, const int* seq_slot, float* out, int n_seqs, int heads,
+                              int key_heads, int value_dim, void* stream) {
+    if (n_seqs <= 0) return 0;
+    if (!rows || !gates || !kq || !state || !cu_seqlens || !seq_slot || !out || heads <= 0 || key_heads <= 0 || heads % key_heads != 0 || value_dim <= 0)
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool narrow = heads * n_seqs * ((value_dim + 31) / 32) < 148 && kSplit <= 16;     // blocks of 16 columns reach more SMs
+    const int tile = narrow ? 16 : 32;
+    dim3 grid(heads, n_seqs, (value_dim + tile - 1) / tile), block(tile * kSplit);
+    if (narrow)
+        tau_launch(delta_rule_kernel<16>, grid, block, 0, s, rows, stride, q_offset, k_offset, v_offset, gates, kq, state, slot_stride, cu_seqlens, seq_slot, out,
+                   heads, key_heads, value_dim);
+    else
+        tau_launch(delta_rule_kernel<32>, grid, block, 0, s, rows, stride, q_offset, k_offset, v_offset, gates, kq, state, slot_stride, cu_seqlens, seq_slot, out,
+                   heads, key_heads, value_dim);
+    return tau_launch_status();
+}

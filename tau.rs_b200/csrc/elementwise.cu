@@ -182,7 +182,7 @@ bool launch_norm_vec(T* values, const T* branch, const int* rows, const float* w
 
 // 16 bytes of gate and of up per thread.
 template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ stacked, T* __restrict__ out, size_t rows, int width) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ stacked, T* __restrict__ out, size_t rows, int width, int relu) {
     grid_dependents_launch();
     grid_dependency_wait();
     constexpr int n = Vec16<T>::n;
@@ -196,14 +196,14 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ stacked, T* __restrict
         unpack16<T>(*reinterpret_cast<const uint4*>(stacked + row * 2 * width + column), gate);
         unpack16<T>(*reinterpret_cast<const uint4*>(stacked + row * 2 * width + width + column), up);
 #pragma unroll
-        for (int i = 0; i < n; ++i) result[i] = gate[i] / (1.0f + expf(-gate[i])) * up[i];
+        for (int i = 0; i < n; ++i) result[i] = (relu ? fmaxf(gate[i], 0.0f) : gate[i] / (1.0f + expf(-gate[i]))) * up[i];
         *reinterpret_cast<uint4*>(out + row * width + column) = pack16<T>(result);
     }
 }
 
-// out[r, c] = silu(in[r, c]) * in[r, width + c]
+// out[r, c] = act(in[r, c]) * in[r, width + c], act being SiLU or (with `relu`) max(z, 0)
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ stacked, T* __restrict__ out, size_t rows, int width) {
+__global__ void silu_mul_kernel(const T* __restrict__ stacked, T* __restrict__ out, size_t rows, int width, int relu) {
     grid_dependents_launch();
     grid_dependency_wait();
     const size_t total = rows * static_cast<size_t>(width);
@@ -213,7 +213,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ stacked, T* __restrict__ o
         const int column = static_cast<int>(index - row * width);
         const float gate = to_float(stacked[row * 2 * width + column]);
         const float up = to_float(stacked[row * 2 * width + width + column]);
-        out[index] = from_float<T>(gate / (1.0f + expf(-gate)) * up);
+        out[index] = from_float<T>((relu ? fmaxf(gate, 0.0f) : gate / (1.0f + expf(-gate))) * up);
     }
 }
 
@@ -275,24 +275,24 @@ TAU_EXPORT int tau_add_rms_norm(int dtype, const void* branch, void* residual, c
     return tau_launch_status();
 }
 
-TAU_EXPORT int tau_silu_mul(int dtype, const void* stacked, void* out, long long rows, int width, void* stream) {
+TAU_EXPORT int tau_silu_mul(int dtype, const void* stacked, void* out, long long rows, int width, int relu, void* stream) {
     if (rows <= 0) return 0;
     if (!stacked || !out || width <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const long long total = rows * width;
     const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
     if (dtype == TAU_F32 && width % 4 == 0) {
-        tau_launch(silu_mul_vec_kernel<float>, dim3(blocks), dim3(256), 0, s, static_cast<const float*>(stacked), static_cast<float*>(out), rows, width);
+        tau_launch(silu_mul_vec_kernel<float>, dim3(blocks), dim3(256), 0, s, static_cast<const float*>(stacked), static_cast<float*>(out), rows, width, relu);
         return tau_launch_status();
     }
     if (dtype == TAU_BF16 && width % 8 == 0) {
-        tau_launch(silu_mul_vec_kernel<bf16>, dim3(blocks), dim3(256), 0, s, static_cast<const bf16*>(stacked), static_cast<bf16*>(out), rows, width);
+        tau_launch(silu_mul_vec_kernel<bf16>, dim3(blocks), dim3(256), 0, s, static_cast<const bf16*>(stacked), static_cast<bf16*>(out), rows, width, relu);
         return tau_launch_status();
     }
     if (dtype == TAU_F32)
-        tau_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, static_cast<const float*>(stacked), static_cast<float*>(out), rows, width);
+        tau_launch(silu_mul_kernel<float>, dim3(blocks), dim3(256), 0, s, static_cast<const float*>(stacked), static_cast<float*>(out), rows, width, relu);
     else if (dtype == TAU_BF16)
-        tau_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, static_cast<const bf16*>(stacked), static_cast<bf16*>(out), rows, width);
+        tau_launch(silu_mul_kernel<bf16>, dim3(blocks), dim3(256), 0, s, static_cast<const bf16*>(stacked), static_cast<bf16*>(out), rows, width, relu);
     else
         return cudaErrorInvalidValue;
     return tau_launch_status();

@@ -86,6 +86,8 @@ _CLASS_OF = {
     "latent_prepare": "attention", "latent_attention": "attention", "latent_expand": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
     "moe_combine": "routing", "diff_prepare": "attention", "diff_attention": "attention", "diff_combine": "attention", "causal_taps": "norm", "gated_add_norm": "norm",
     "side_gate": "activation", "unit_add_mix": "norm", "norm_rows": "norm", "relu_squared": "activation",
+    "short_conv": "recurrence", "delta_prepare": "recurrence", "delta_rule": "recurrence", "selective_scan": "recurrence",
+    "masked_prepare": "attention", "masked_attention": "attention",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
 
@@ -143,15 +145,17 @@ def _int_vector(tensor: torch.Tensor, what: str) -> None:
 
 
 # ---------------------------------------------------------------------------- elementwise
-def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0) -> None:
+    """`out[i] = table[tokens[i]] * scale`; a scale other than 1 needs a 32-bit output."""
     _on_device(tokens, table, out)
     _int_vector(tokens, "token ids")
     _require(out.shape == (tokens.shape[0], table.shape[1]), "output must be [tokens, width]")
-    if out.dtype == torch.float32 and table.dtype != torch.float32:   # rows widened into a 32-bit residual stream
+    _require(scale == 1.0 or out.dtype == torch.float32, "scaled rows go into a 32-bit residual stream")
+    if out.dtype == torch.float32 and (table.dtype != torch.float32 or scale != 1.0):   # rows widened into a 32-bit residual stream
         _require(table.is_contiguous() and out.is_contiguous(), "table and output must be contiguous")
         library = build.load_library("stream32.cu")
         return _check(library.tau_embedding_f32(_code(table), _pointer(tokens), _pointer(table), _pointer(out), ctypes.c_int(tokens.shape[0]),
-                                                ctypes.c_int(table.shape[1]), ctypes.c_int(table.shape[0]), _stream()), "embedding")
+                                                ctypes.c_int(table.shape[1]), ctypes.c_int(table.shape[0]), ctypes.c_float(scale), _stream()), "embedding")
     _require(table.dtype == out.dtype and table.is_contiguous() and out.is_contiguous(), "table and output must match")
     library = build.load_library("elementwise.cu")
     _check(library.tau_embedding(_code(table), _pointer(tokens), _pointer(table), _pointer(out), ctypes.c_int(tokens.shape[0]),
@@ -229,13 +233,14 @@ def stream_add_norm(stream, branches, weight, eps: float, out, rows=None, update
                                        _stream()), "stream_add_norm")
 
 
-def gated_group_norm(values, weight, gate, out, groups: int, eps: float, normalize: bool) -> None:
+def gated_group_norm(values, weight, gate, out, groups: int, eps: float, normalize: bool, silu_gate: bool = False) -> None:
     """`values` [rows, width] in 32-bit; with `normalize` each of the `groups` equal parts of a row is divided by its root
-    mean square (eps inside the root); then times `weight` (float32 [width] or None), times `sigmoid(gate)` (the output's
-    dtype, [rows, width], rows any distance apart, or None); rounded once to the output's dtype."""
+    mean square (eps inside the root); then times `weight` (float32 [width] or None), times `sigmoid(gate)` or, with `silu_gate`,
+    `gate * sigmoid(gate)` (the output's dtype, [rows, width], rows any distance apart, or None); rounded once to the output's
+    dtype.  The output's rows may lie any distance apart too (a column range of a wider tensor)."""
     _on_device(values, weight, gate, out)
     rows, width = values.shape
-    _require(values.dtype == torch.float32 and values.is_contiguous() and out.is_contiguous() and out.shape == values.shape,
+    _require(values.dtype == torch.float32 and values.is_contiguous() and out.stride(1) == 1 and out.shape == values.shape,
              "values must be contiguous float32 and the output of the same shape")
     _require(groups > 0 and width % groups == 0, "the groups must divide the width")
     _f32_vector(weight, width, "the weight")
@@ -243,13 +248,13 @@ def gated_group_norm(values, weight, gate, out, groups: int, eps: float, normali
         _require(gate.dtype == out.dtype and gate.shape == values.shape and gate.stride(1) == 1, "the gate must have the output's dtype and shape")
     library = build.load_library("stream32.cu")
     _check(library.tau_gated_group_norm(_code(out), _pointer(values), _pointer(weight), _pointer(gate),
-                                        ctypes.c_longlong(0 if gate is None else gate.stride(0)), _pointer(out), ctypes.c_int(rows),
+                                        ctypes.c_longlong(0 if gate is None else gate.stride(0)), _pointer(out), ctypes.c_longlong(out.stride(0)), ctypes.c_int(rows),
                                         ctypes.c_int(groups), ctypes.c_int(width // groups), ctypes.c_float(eps), ctypes.c_int(1 if normalize else 0),
-                                        _stream()), "gated_group_norm")
+                                        ctypes.c_int(1 if silu_gate else 0), _stream()), "gated_group_norm")
 
 
-def silu_mul(stacked, out) -> None:
-    """`out[r, c] = silu(stacked[r, c]) * stacked[r, width + c]`."""
+def silu_mul(stacked, out, relu: bool = False) -> None:
+    """`out[r, c] = silu(stacked[r, c]) * stacked[r, width + c]`; with `relu` the activation is `max(z, 0)` instead."""
     _on_device(stacked, out)
     width = out.shape[-1]
     _require(stacked.shape[-1] == 2 * width and stacked.shape[0] == out.shape[0] and stacked.dtype == out.dtype,
@@ -257,7 +262,7 @@ def silu_mul(stacked, out) -> None:
     _require(stacked.is_contiguous() and out.is_contiguous(), "tensors must be contiguous")
     library = build.load_library("elementwise.cu")
     _check(library.tau_silu_mul(_code(out), _pointer(stacked), _pointer(out), ctypes.c_longlong(out.shape[0]), ctypes.c_int(width),
-                                _stream()), "silu_mul")
+                                ctypes.c_int(1 if relu else 0), _stream()), "silu_mul")
 
 
 # ---------------------------------------------------------------------------- products
@@ -1103,6 +1108,173 @@ def linear_recurrence(q, k, v, gates, decays, state, cu_seqlens, seq_slot, out, 
         ctypes.c_int(1 if silu else 0), _stream()), "linear_recurrence", 2 if exponential else 1)
 
 
+# ---------------------------------------------------------------------------- short convolutions, delta rule, selective scan
+def short_conv(x, weight, bias, state, step, out, silu: bool = True, update: bool = True) -> None:
+    """`out[t, c] = act(bias[c] + sum_j weight[j, c] * x[t - (taps - 1) + j, c])` over each sequence's run of the step (`weight`
+    float32 [taps, channels], tap by tap, the last tap weighing the token itself; `bias` float32 [channels] or None; `act` SiLU or
+    none); rows before the run's first token come from `state[slot]` ([slots, taps - 1, channels] float32: the sequence's last
+    inputs, zeros at its start).  `x` and `out` may be column ranges of wider tensors; `out` is float32 or of `x`'s dtype.  With
+    `update` the state then becomes the last `taps - 1` inputs of each sequence (a second launch, or the same one where every
+    sequence brings one token)."""
+    _on_device(x, weight, bias, state, out)
+    tokens, channels = x.shape
+    taps = weight.shape[0]
+    _require(x.stride(1) == 1 and out.stride(1) == 1 and out.shape == x.shape and out.dtype in (torch.float32, x.dtype), "the output must match the input's shape")
+    _require(weight.dtype == torch.float32 and weight.shape == (taps, channels) and weight.is_contiguous() and taps >= 1, "the taps must be float32 [taps, channels]")
+    _f32_vector(bias, channels, "the bias")
+    if taps > 1:
+        _require(state is not None and state.dtype == torch.float32 and state.shape[1:] == (taps - 1, channels) and state.is_contiguous(),
+                 "the state must be float32 [slots, taps - 1, channels]")
+    update = update and taps > 1
+    single = bool(getattr(step, "all_single", False)) and tokens == step.n_seqs
+    library = build.load_library("short_conv.cu")
+    _check(library.tau_short_conv(_code(x), _code(out), _pointer(x), ctypes.c_longlong(x.stride(0)), _pointer(weight), _pointer(bias), _pointer(state),
+                                  _pointer(step.token_seq), _pointer(step.cu_seqlens), _pointer(step.seq_slot), _pointer(out), ctypes.c_longlong(out.stride(0)),
+                                  ctypes.c_int(tokens), ctypes.c_int(step.n_seqs), ctypes.c_int(channels), ctypes.c_int(taps), ctypes.c_int(1 if silu else 0),
+                                  ctypes.c_int(1 if update else 0), ctypes.c_int(1 if single else 0), _stream()),
+           "short_conv", 2 if update and not single else 1)
+
+
+DELTA_MAX_KEY_DIM = 512
+
+
+def delta_prepare(rows, q_offset: int, k_offset: int, pre, a_log, dt_bias, gates, kq, n_heads: int, n_key_heads: int, key_dim: int) -> None:
+    """In place on `rows` (float32 [tokens, width]): the queries (`n_key_heads * key_dim` columns from `q_offset`) and keys (from
+    `k_offset`) become unit vectors per head, `x / sqrt(sum(x^2) + 1e-6)`, the queries also times `key_dim ** -0.5`.
+    `kq` [tokens, n_key_heads] receives `k . q` of the results.  `pre` float32 [tokens, 2 * n_heads] holds per value head the
+    pre-activation of beta, then of the decay's step; `gates` [tokens, n_heads, 2] receives
+    `(exp(-exp(a_log) * softplus(step + dt_bias)), sigmoid(beta))`."""
+    _on_device(rows, pre, a_log, dt_bias, gates, kq)
+    tokens = rows.shape[0]
+    _require(rows.dtype == torch.float32 and rows.stride(1) == 1 and max(q_offset, k_offset) + n_key_heads * key_dim <= rows.shape[1], "rows must be float32 and hold q and k")
+    _require(pre.dtype == torch.float32 and pre.shape == (tokens, 2 * n_heads) and pre.is_contiguous(), "the gates' pre-activations must be float32 [tokens, 2 * heads]")
+    _f32_vector(a_log, n_heads, "A_log")
+    _f32_vector(dt_bias, n_heads, "dt_bias")
+    _require(gates.dtype == torch.float32 and gates.shape == (tokens, n_heads, 2) and gates.is_contiguous(), "gates must be float32 [tokens, heads, 2]")
+    _require(kq.dtype == torch.float32 and kq.shape == (tokens, n_key_heads) and kq.is_contiguous(), "kq must be float32 [tokens, key heads]")
+    _require(1 <= key_dim <= DELTA_MAX_KEY_DIM and n_heads % n_key_heads == 0, f"key_dim must lie between 1 and {DELTA_MAX_KEY_DIM}, and the key heads divide the heads")
+    library = build.load_library("delta_rule.cu", (f"TAU_KEY_DIM={key_dim}",))
+    _check(library.tau_delta_prepare(_pointer(rows), ctypes.c_longlong(rows.stride(0)), ctypes.c_int(q_offset), ctypes.c_int(k_offset), _pointer(pre),
+                                     _pointer(a_log), _pointer(dt_bias), _pointer(gates), _pointer(kq), ctypes.c_int(tokens), ctypes.c_int(n_heads),
+                                     ctypes.c_int(n_key_heads), ctypes.c_float(key_dim ** -0.5), _stream()), "delta_prepare")
+
+
+def delta_rule(rows, q_offset: int, k_offset: int, v_offset: int, gates, kq, state, cu_seqlens, seq_slot, out, n_heads: int, n_key_heads: int,
+               key_dim: int, value_dim: int) -> None:
+    """Advances the gated delta rule of every (sequence, head) over the sequence's new tokens: `S <- g S; u = beta (v - S^T k);
+    S <- S + k u^T; o = S^T q`.  `rows` as `delta_prepare` left them, with the values (`n_heads * value_dim` columns) from
+    `v_offset`; `gates` [tokens, n_heads, 2] = (g, beta); `kq` [tokens, n_key_heads]; `state` float32 [slots, n_heads * value_dim *
+    key_dim], updated in place; `out` float32 [tokens, n_heads * value_dim]."""
+    _on_device(rows, gates, kq, state, cu_seqlens, seq_slot, out)
+    tokens = rows.shape[0]
+    _require(rows.dtype == torch.float32 and rows.stride(1) == 1 and v_offset + n_heads * value_dim <= rows.shape[1], "rows must be float32 and hold q, k and v")
+    _require(gates.dtype == torch.float32 and gates.shape == (tokens, n_heads, 2) and gates.is_contiguous(), "gates must be float32 [tokens, heads, 2]")
+    _require(kq.dtype == torch.float32 and kq.shape == (tokens, n_key_heads) and kq.is_contiguous(), "kq must be float32 [tokens, key heads]")
+    _require(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] == n_heads * value_dim * key_dim,
+             f"the state must be float32 [slots, {n_heads * value_dim * key_dim}]")
+    _require(out.shape == (tokens, n_heads * value_dim) and out.dtype == torch.float32 and out.is_contiguous(), "the output must be float32 [tokens, heads * value_dim]")
+    _require(1 <= key_dim <= DELTA_MAX_KEY_DIM and n_heads % n_key_heads == 0, f"key_dim must lie between 1 and {DELTA_MAX_KEY_DIM}, and the key heads divide the heads")
+    _int_vector(cu_seqlens, "cu_seqlens")
+    _int_vector(seq_slot, "seq_slot")
+    n_seqs = seq_slot.numel()
+    _require(cu_seqlens.numel() == n_seqs + 1, "one run per sequence")
+    library = build.load_library("delta_rule.cu", (f"TAU_KEY_DIM={key_dim}",))
+    _check(library.tau_delta_rule(_pointer(rows), ctypes.c_longlong(rows.stride(0)), ctypes.c_int(q_offset), ctypes.c_int(k_offset), ctypes.c_int(v_offset),
+                                  _pointer(gates), _pointer(kq), _pointer(state), ctypes.c_longlong(state.stride(0)), _pointer(cu_seqlens), _pointer(seq_slot),
+                                  _pointer(out), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_key_heads), ctypes.c_int(value_dim), _stream()),
+           "delta_rule")
+
+
+SCAN_MAX_STATES = 256
+
+
+def selective_scan(x, z, pre, bc, a_log, skip, state, cu_seqlens, seq_slot, out) -> None:
+    """Per channel `c` and state `n`, over each sequence's new tokens: `step = softplus(pre[t, c])`;
+    `S[c, n] <- exp(step * A[c, n]) * S[c, n] + step * x[t, c] * B[t, n]` with `A = -exp(a_log)`; `y = sum_n S[c, n] * C[t, n] +
+    skip[c] * x[t, c]`; `out[t, c] = y * silu(z[t, c])`.  `x`, `z` [tokens, channels] (column ranges of wider tensors allowed),
+    `pre` float32 [tokens, channels], `bc` float32 [tokens, 2 * states] (B, then C), `a_log` float32 [channels, states],
+    `state` float32 [slots, channels * states], updated in place; `out` [tokens, channels] of `x`'s dtype."""
+    _on_device(x, z, pre, bc, a_log, skip, state, cu_seqlens, seq_slot, out)
+    tokens, channels = x.shape
+    states = a_log.shape[1]
+    _require(x.stride(1) == 1 and z.stride(1) == 1 and z.shape == x.shape and z.dtype == x.dtype == out.dtype and out.shape == x.shape and out.is_contiguous(),
+             "x, z and the output must be [tokens, channels] of one dtype")
+    _require(pre.dtype == torch.float32 and pre.shape == x.shape and pre.is_contiguous(), "the steps' pre-activations must be float32 [tokens, channels]")
+    _require(bc.dtype == torch.float32 and bc.shape == (tokens, 2 * states) and bc.is_contiguous(), "B and C must be float32 [tokens, 2 * states]")
+    _require(a_log.dtype == torch.float32 and a_log.shape == (channels, states) and a_log.is_contiguous() and 1 <= states <= SCAN_MAX_STATES,
+             f"A_log must be float32 [channels, states] with at most {SCAN_MAX_STATES} states")
+    _f32_vector(skip, channels, "the skip weight")
+    _require(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] == channels * states,
+             f"the state must be float32 [slots, {channels * states}]")
+    _int_vector(cu_seqlens, "cu_seqlens")
+    _int_vector(seq_slot, "seq_slot")
+    n_seqs = seq_slot.numel()
+    _require(cu_seqlens.numel() == n_seqs + 1, "one run per sequence")
+    library = build.load_library("selective_scan.cu", (f"TAU_SCAN_STATES={states}",))
+    _check(library.tau_selective_scan(_code(x), _pointer(x), ctypes.c_longlong(x.stride(0)), _pointer(z), ctypes.c_longlong(z.stride(0)), _pointer(pre),
+                                      _pointer(bc), _pointer(a_log), _pointer(skip), _pointer(state), _pointer(cu_seqlens), _pointer(seq_slot), _pointer(out),
+                                      ctypes.c_int(n_seqs), ctypes.c_int(channels), _stream()), "selective_scan")
+
+
+# ---------------------------------------------------------------------------- attention over cached rows with a mask and a sink
+MASKED_MAX_VALUE_DIM = 512
+
+
+def masked_prepare(projected, q_weight, k_weight, eps: float, frequency, rotary_dim: int, magnitude: float, queries, rows, positions, token_seq,
+                   page_rows, n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_rows: bool = True) -> None:
+    """`projected` [tokens, >= n_heads * dim + n_kv_heads * (dim + vdim)] holds queries, keys and values side by side.  With weights
+    (float32 [n_heads * dim] and [n_kv_heads * dim]) the queries, and the keys, are divided by the root mean square over their
+    whole projection (eps inside the root) and multiplied by the weight.  In every head element `i` of the first `rotary_dim` is
+    turned together with element `i + rotary_dim / 2` by `position * frequency[i]`, sine and cosine times `magnitude`.  Queries go
+    to `queries` [tokens, n_heads, dim]; with `write_rows` keys and values go to the token's row of the cache pages `rows`
+    [pages, 64, n_kv_heads * (dim + vdim)] as [keys of all heads | values]."""
+    _on_device(projected, q_weight, k_weight, frequency, queries, rows, positions, token_seq, page_rows)
+    tokens = projected.shape[0]
+    row_width = n_kv_heads * (dim + vdim)
+    _require(projected.shape[1] >= n_heads * dim + row_width and projected.stride(1) == 1, "the projection is too narrow")
+    _require(queries.shape == (tokens, n_heads, dim) and queries.is_contiguous() and queries.dtype == projected.dtype, "queries must be [tokens, n_heads, dim]")
+    _f32_vector(q_weight, n_heads * dim, "the query norm weight")
+    _f32_vector(k_weight, n_kv_heads * dim, "the key norm weight")
+    _require(rotary_dim % 2 == 0 and 0 <= rotary_dim <= dim, "rotary_dim must be even and at most dim")
+    if rotary_dim:
+        _f32_vector(frequency, rotary_dim // 2, "the rotation's frequencies")
+    _int_vector(positions, "positions")
+    if write_rows:
+        _int_vector(token_seq, "token_seq")
+        _require(rows.shape[1:] == (PAGE_TOKENS, row_width) and rows.is_contiguous() and rows.dtype == projected.dtype, "cache rows must be [pages, 64, row width]")
+        _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("masked_attention.cu")
+    _check(library.tau_masked_prepare(
+        _code(projected), _pointer(projected), ctypes.c_longlong(projected.stride(0)), _pointer(q_weight), _pointer(k_weight), ctypes.c_float(eps),
+        _pointer(frequency if rotary_dim else None), ctypes.c_int(rotary_dim), ctypes.c_float(magnitude), _pointer(queries), _pointer(rows if write_rows else None),
+        _pointer(positions), _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1] if write_rows else 0), ctypes.c_int(PAGE_TOKENS),
+        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_int(1 if write_rows else 0),
+        _stream()), "masked_prepare")
+
+
+def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim: int, scale: float, window: int = 0, chunk: int = 0, sink: bool = False,
+                     out_scale: float = 1.0) -> None:
+    """Causal softmax attention of every token over the cached rows of its sequence: within `window` positions (if not 0), or
+    within the token's own chunk of `chunk` positions counted from position 0 (if not 0); with `sink` the softmax's denominator has
+    one added.  `out` [tokens, n_heads * vdim] (rows any distance apart) receives the result times `out_scale`.  Scores, weights
+    and sums are 32-bit."""
+    _on_device(queries, rows, out, page_rows)
+    tokens, n_heads, dim = queries.shape
+    row_width = n_kv_heads * (dim + vdim)
+    _require(queries.is_contiguous() and out.shape == (tokens, n_heads * vdim) and out.stride(1) == 1 and out.dtype == queries.dtype == rows.dtype,
+             "queries must be [tokens, n_heads, dim] and the output [tokens, n_heads * vdim]")
+    _require(rows.shape[1:] == (PAGE_TOKENS, row_width) and rows.is_contiguous(), "cache rows must be [pages, 64, row width]")
+    _require(vdim <= MASKED_MAX_VALUE_DIM, f"values may have at most {MASKED_MAX_VALUE_DIM} elements per head")
+    _require(not (window and chunk), "a window or a chunk, not both")
+    _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    library = build.load_library("masked_attention.cu")
+    _check(library.tau_masked_attention(
+        _code(queries), _pointer(queries), _pointer(rows), _pointer(out), ctypes.c_longlong(out.stride(0)), _pointer(step.positions), _pointer(step.token_seq),
+        _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
+        ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk), ctypes.c_int(1 if sink else 0),
+        ctypes.c_float(out_scale), _stream()), "masked_attention")
+
+
 # ---------------------------------------------------------------------------- routed experts
 def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, shared_gate, top: int, softmax: bool = False,
               renormalize: bool = False, logit_bias=None) -> None:
@@ -1129,10 +1301,11 @@ def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, s
                                  _stream()), "moe_route")
 
 
-def moe_gate_up(hidden, gate_up, chosen, inner, interleave: int = 0) -> None:
-    """`inner[token, place] = silu(gate_e @ h) * (up_e @ h)` with `e = chosen[token, place]`; `gate_up` [experts, 2 * I, width]
-    holds each expert's gate rows, then its up rows, or with `interleave` groups of that many gate rows each followed by
-    their up rows (what `linear_gated` reads); `inner` [tokens, top, I]."""
+def moe_gate_up(hidden, gate_up, chosen, inner, interleave: int = 0, input_weights=None) -> None:
+    """`inner[token, place] = silu(gate_e @ x) * (up_e @ x)` with `e = chosen[token, place]` and `x = h`, or
+    `x = input_weights[token, place] * h` (float32 [tokens, top]; the weight multiplies the two products' 32-bit sums); `gate_up`
+    [experts, 2 * I, width] holds each expert's gate rows, then its up rows, or with `interleave` groups of that many gate rows
+    each followed by their up rows (what `linear_gated` reads); `inner` [tokens, top, I]."""
     _require(interleave == 0 or inner.shape[2] % interleave == 0, "the interleaved groups must divide the expert's width")
     _on_device(hidden, gate_up, chosen, inner)
     tokens, width = hidden.shape
@@ -1141,22 +1314,25 @@ def moe_gate_up(hidden, gate_up, chosen, inner, interleave: int = 0) -> None:
              "tensors must be contiguous and of one dtype")
     _require(gate_up.shape[1:] == (2 * size, width) and inner.shape[0] == tokens and chosen.shape == (tokens, top) and chosen.dtype == torch.int32
              and chosen.is_contiguous(), "shapes must be [T,W], [E,2I,W], [T,top] -> [T,top,I]")
+    if input_weights is not None:
+        _on_device(input_weights)
+        _require(input_weights.shape == (tokens, top) and input_weights.dtype == torch.float32 and input_weights.is_contiguous(), "input weights must be float32 [tokens, top]")
     library = build.load_library("moe.cu")
-    _check(library.tau_moe_gate_up(_code(hidden), _pointer(hidden), _pointer(gate_up), _pointer(chosen), _pointer(inner), ctypes.c_int(tokens),
+    _check(library.tau_moe_gate_up(_code(hidden), _pointer(hidden), _pointer(gate_up), _pointer(chosen), _pointer(input_weights), _pointer(inner), ctypes.c_int(tokens),
                                    ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top), ctypes.c_int(interleave), _stream()), "moe_gate_up")
 
 
 def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out) -> None:
     """`out[token] = sum_place weights[token, place] * (down_e @ inner[token, place]) + shared_gate[token] * shared_out[token]`,
-    float32 [tokens, width]; `down` [experts, width, I]; `shared_out` (the activations' dtype) and `shared_gate` (float32
-    [tokens]; None: 1) are optional."""
+    float32 [tokens, width]; `down` [experts, width, I]; `weights` (None: 1), `shared_out` (the activations' dtype) and
+    `shared_gate` (float32 [tokens]; None: 1) are optional."""
     _on_device(inner, down, chosen, weights, shared_out, shared_gate, out)
     tokens, top, size = inner.shape
     width = down.shape[1]
     _require(inner.is_contiguous() and down.is_contiguous() and inner.dtype == down.dtype and down.shape[2] == size, "down must be [experts, width, I]")
     _require(out.shape == (tokens, width) and out.dtype == torch.float32 and out.is_contiguous(), "the output must be float32 [tokens, width]")
-    _require(chosen.shape == (tokens, top) and chosen.dtype == torch.int32 and chosen.is_contiguous() and weights.shape == (tokens, top)
-             and weights.dtype == torch.float32 and weights.is_contiguous(), "chosen and weights must be [tokens, top]")
+    _require(chosen.shape == (tokens, top) and chosen.dtype == torch.int32 and chosen.is_contiguous() and (weights is None or (weights.shape == (tokens, top)
+             and weights.dtype == torch.float32 and weights.is_contiguous())), "chosen and weights must be [tokens, top]")
     if shared_out is not None:
         _require(shared_out.shape == (tokens, width) and shared_out.dtype == inner.dtype and shared_out.is_contiguous(), "the shared output must be [tokens, width]")
     if shared_gate is not None:
@@ -1180,26 +1356,29 @@ def moe_sort(chosen, experts: int, offsets, order, position) -> None:
                                 _stream()), "moe_sort")
 
 
-def moe_gather(hidden, order, top: int, gathered) -> None:
-    """`gathered[i] = hidden[order[i] // top]`."""
-    _on_device(hidden, order, gathered)
+def moe_gather(hidden, order, top: int, gathered, input_weights=None) -> None:
+    """`gathered[i] = hidden[order[i] // top]`, times `input_weights.view(-1)[order[i]]` (float32, one per pair) if given."""
+    _on_device(hidden, order, gathered, input_weights)
     pairs, width = gathered.shape
     _require(hidden.is_contiguous() and gathered.is_contiguous() and hidden.dtype == gathered.dtype and hidden.shape[1] == width
              and order.dtype == torch.int32 and order.numel() == pairs, "gathered must be [pairs, width] of the input's dtype")
+    if input_weights is not None:
+        _require(input_weights.dtype == torch.float32 and input_weights.numel() == pairs and input_weights.is_contiguous(), "one float32 input weight per pair")
     library = build.load_library("moe.cu")
-    _check(library.tau_moe_gather(_code(hidden), _pointer(hidden), _pointer(order), _pointer(gathered), ctypes.c_int(pairs), ctypes.c_int(width),
+    _check(library.tau_moe_gather(_code(hidden), _pointer(hidden), _pointer(order), _pointer(input_weights), _pointer(gathered), ctypes.c_int(pairs), ctypes.c_int(width),
                                   ctypes.c_int(top), _stream()), "moe_gather")
 
 
 def moe_combine(rows, position, weights, shared_out, shared_gate, out) -> None:
     """`out[token] = sum_place weights[token, place] * rows[position[token, place]] + shared_gate[token] * shared_out[token]`;
-    `rows` float32 [pairs, width], `out` float32 [tokens, width]."""
+    `rows` float32 [pairs, width], `out` float32 [tokens, width]; `weights` None: 1."""
     _on_device(rows, position, weights, shared_out, shared_gate, out)
     tokens, width = out.shape
-    top = weights.shape[1]
+    top = position.numel() // tokens
     _require(rows.dtype == torch.float32 == out.dtype and rows.shape == (tokens * top, width) and rows.is_contiguous() and out.is_contiguous(),
              "rows must be float32 [tokens * top, width]")
-    _require(position.dtype == torch.int32 and position.numel() == tokens * top and weights.dtype == torch.float32 and weights.is_contiguous(),
+    _require(position.dtype == torch.int32 and position.numel() == tokens * top and (weights is None or (weights.dtype == torch.float32 and weights.is_contiguous()
+                                                                                            and weights.numel() == tokens * top)),
              "one position and one weight per pair")
     if shared_out is not None:
         _require(shared_out.shape == (tokens, width) and shared_out.is_contiguous(), "the shared output must be [tokens, width]")

@@ -1,0 +1,217 @@
+// Grouped-query softmax attention over cached rows for heads of any sizes, with the mask and the denominator as parameters:
+//
+//   * key and value sizes may differ (`dim`, `vdim`); one cached row per position holds [kv_heads x key | kv_heads x value];
+//   * a query at position i sees key j <= i if j > i - window (`window` > 0), or if j lies in i's chunk, floor(j / chunk) ==
+//     floor(i / chunk) (`chunk` > 0; chunks are counted from position 0 of the sequence), or always (both 0);
+//   * `sink`: the denominator of the softmax has exp(0) added (a key with score 0 and no value);
+//   * the result is multiplied by `out_scale` before its one rounding; output rows may lie any distance apart.
+//
+//   prepare:    q and k divided by the root mean square over the WHOLE projection (all heads together; eps inside the root) and
+//               multiplied by a weight of that size (or left as they are without weights); then in every head the first `rotary`
+//               elements are turned: element i is paired with element i + rotary / 2, by the angle position * frequency[i], with
+//               sine and cosine multiplied by `magnitude`; queries to [tokens, heads, dim], keys and values to the token's row.
+//   attention:  a warp per (token, head): 32 keys at a time, a lane scores one key, then every lane sums its own value columns;
+//               running maximum (never below the sink's 0 when there is one) and sum; scores, weights and sums in 32-bit.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kWarps = 8;
+constexpr int kMaxOwned = 16;     // value columns per lane: vdim <= 512
+
+// grid: tokens; block kWarps * 32.  projected row: [heads * dim | kv_heads * dim | kv_heads * vdim] from its first column on.
+// Dynamic shared memory: rotary / 2 float2 (cosine, sine).
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+masked_prepare_kernel(const T* __restrict__ projected, long long projected_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
+                      float eps, const float* __restrict__ frequency, int rotary, float magnitude, T* __restrict__ queries, T* __restrict__ rows,
+                      const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
+                      int page_tokens, int heads, int kv_heads, int dim, int vdim, int write_rows) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ float2 turns[];
+    __shared__ float scratch[33];
+    const int token = blockIdx.x;
+    const int position = positions[token];
+    const int half = rotary / 2;
+    for (int pair = threadIdx.x; pair < half; pair += blockDim.x) {
+        float sine, cosine;
+        sincosf(static_cast<float>(position) * frequency[pair], &sine, &cosine);
+        turns[pair] = make_float2(cosine * magnitude, sine * magnitude);
+    }
+    const T* source = projected + static_cast<size_t>(token) * projected_stride;
+    const int q_width = heads * dim, k_width = kv_heads * dim;
+    float q_inverse = 1.0f, k_inverse = 1.0f;
+    if (q_weight) {
+        float squares = 0.0f;
+        for (int column = threadIdx.x; column < q_width; column += blockDim.x) {
+            const float value = to_float(source[column]);
+            squares = fmaf(value, value, squares);
+        }
+        q_inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(q_width) + eps);
+    }
+    if (k_weight && write_rows) {
+        float squares = 0.0f;
+        for (int column = threadIdx.x; column < k_width; column += blockDim.x) {
+            const float value = to_float(source[q_width + column]);
+            squares = fmaf(value, value, squares);
+        }
+        k_inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(k_width) + eps);
+    }
+    __syncthreads();      // the turns are complete
+    T* row = nullptr;
+    if (write_rows) {
+        const int page = page_rows[static_cast<size_t>(token_seq[token]) * page_stride + position / page_tokens];
+        row = rows + (static_cast<size_t>(page) * page_tokens + position % page_tokens) * (static_cast<size_t>(kv_heads) * (dim + vdim));
+    }
+    // Items: within each head, the `half` rotated pairs, then the dim - rotary elements that pass.
+    const int per_head = half + (dim - rotary);
+    const int q_items = heads * per_head, items = q_items + (write_rows ? kv_heads * per_head : 0);
+    for (int item = threadIdx.x; item < items; item += blockDim.x) {
+        const bool is_query = item < q_items;
+        const int index = is_query ? item : item - q_items;
+        const int head = index / per_head, within = index % per_head;
+        const T* from = source + (is_query ? 0 : q_width) + head * dim;
+        const float* weight = is_query ? q_weight : k_weight;
+        const float inverse = is_query ? q_inverse : k_inverse;
+        T* target = (is_query ? queries + static_cast<size_t>(token) * q_width : row) + head * dim;
+        if (within < half) {
+            const int first = within, second = within + half;
+            float u = to_float(from[first]) * inverse, w = to_float(from[second]) * inverse;
+            if (weight) {
+                u *= weight[head * dim + first];
+                w *= weight[head * dim + second];
+            }
+            const float2 turn = turns[within];
+            target[first] = from_float<T>(u * turn.x - w * turn.y);
+            target[second] = from_float<T>(w * turn.x + u * turn.y);
+        } else {
+            const int column = rotary + (within - half);
+            float u = to_float(from[column]) * inverse;
+            if (weight) u *= weight[head * dim + column];
+            target[column] = from_float<T>(u);
+        }
+    }
+    if (write_rows) {
+        const T* values = source + q_width + k_width;
+        T* target = row + k_width;
+        for (int column = threadIdx.x; column < kv_heads * vdim; column += blockDim.x) target[column] = values[column];
+    }
+}
+
+// grid: (tokens, ceil(heads / kWarps)); a warp per head.  Dynamic shared memory: kWarps * dim floats (the queries).
+template <typename T>
+__global__ void __launch_bounds__(kWarps * 32)
+masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ rows, T* __restrict__ out, long long out_stride,
+                        const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
+                        int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    extern __shared__ float shared[];
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.y * kWarps + warp;
+    if (head >= heads) return;
+    float* query = shared + static_cast<size_t>(warp) * dim;
+    const T* q_source = queries + (static_cast<size_t>(token) * heads + head) * dim;
+    for (int column = lane; column < dim; column += 32) query[column] = to_float(q_source[column]) * scale;
+    __syncwarp();
+    const int position = positions[token];
+    const int* pages = page_rows + static_cast<size_t>(token_seq[token]) * page_stride;
+    const int group = head / (heads / kv_heads);
+    const int row_width = kv_heads * (dim + vdim);
+    const int key_offset = group * dim, value_offset = kv_heads * dim + group * vdim;
+    int first_key = 0;
+    if (window > 0 && position - window + 1 > 0) first_key = position - window + 1;
+    if (chunk > 0) first_key = position / chunk * chunk;
+    float top = sink ? 0.0f : -INFINITY, sum = sink ? 1.0f : 0.0f;       // the sink: a weight of exp(0 - top) that carries no value
+    float acc[kMaxOwned];
+#pragma unroll
+    for (int i = 0; i < kMaxOwned; ++i) acc[i] = 0.0f;
+    for (int base = first_key; base <= position; base += 32) {
+        const int key = base + lane;
+        const bool valid = key <= position;
+        long long row_index = 0;
+        float score = -INFINITY;
+        if (valid) {
+            row_index = static_cast<long long>(pages[key / page_tokens]) * page_tokens + key % page_tokens;
+            const T* k = rows + row_index * row_width + key_offset;
+            float a = 0.0f, b = 0.0f;
+            int column = 0;
+            for (; column + 1 < dim; column += 2) {
+                a = fmaf(query[column], to_float(k[column]), a);
+                b = fmaf(query[column + 1], to_float(k[column + 1]), b);
+            }
+            if (column < dim) a = fmaf(query[column], to_float(k[column]), a);
+            score = a + b;
+        }
+        const float new_top = fmaxf(top, warp_max(score));       // finite: the block holds at least one key
+        const float p = valid ? expf(score - new_top) : 0.0f;
+        const float keep = expf(top - new_top);                   // exp(-inf) = 0 the first time without a sink
+        sum = sum * keep + warp_sum(p);
+        top = new_top;
+#pragma unroll
+        for (int i = 0; i < kMaxOwned; ++i) acc[i] *= keep;
+        const int count = position - base + 1 < 32 ? position - base + 1 : 32;
+        for (int j = 0; j < count; ++j) {
+            const float w = __shfl_sync(0xffffffffu, p, j);
+            const long long index = __shfl_sync(0xffffffffu, row_index, j);
+            const T* v = rows + index * row_width + value_offset;
+#pragma unroll
+            for (int i = 0; i < kMaxOwned; ++i) {
+                const int column = lane + 32 * i;
+                if (column < vdim) acc[i] = fmaf(w, to_float(v[column]), acc[i]);
+            }
+        }
+    }
+    const float factor = out_scale / sum;
+#pragma unroll
+    for (int i = 0; i < kMaxOwned; ++i) {
+        const int column = lane + 32 * i;
+        if (column < vdim) out[static_cast<size_t>(token) * out_stride + head * vdim + column] = from_float<T>(acc[i] * factor);
+    }
+}
+
+}  // namespace
+
+TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
+                                  const float* frequency, int rotary, float magnitude, void* queries, void* rows, const int* positions, const int* token_seq,
+                                  const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                  int write_rows, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!projected || !queries || !positions || heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || rotary < 0 || rotary > dim || rotary % 2 != 0 ||
+        (rotary && !frequency) || (write_rows && (!rows || !token_seq || !page_rows)))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t bytes = static_cast<size_t>(rotary / 2) * sizeof(float2);
+    if (bytes > 40 * 1024) return cudaErrorInvalidValue;
+#define TAU_PREPARE(T)                                                                                                                            \
+    tau_launch(masked_prepare_kernel<T>, dim3(tokens), dim3(kWarps * 32), bytes, s, static_cast<const T*>(projected), projected_stride, q_weight, k_weight, eps, \
+               frequency, rotary, magnitude, static_cast<T*>(queries), static_cast<T*>(rows), positions, token_seq, page_rows, page_stride, page_tokens, heads,   \
+               kv_heads, dim, vdim, write_rows)
+    if (dtype == TAU_F32) TAU_PREPARE(float);
+    else if (dtype == TAU_BF16) TAU_PREPARE(bf16);
+    else return cudaErrorInvalidValue;
+#undef TAU_PREPARE
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* rows, void* out, long long out_stride, const int* positions,
+                                    const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
+                                    int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, void* stream) {
+    if (tokens <= 0) return 0;
+    if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim <= 0 ||
+        vdim <= 0 || vdim > 32 * kMaxOwned || window < 0 || chunk < 0 || (window > 0 && chunk > 0))
+        return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const size_t bytes = static_cast<size_t>(kWarps) * dim * sizeof(float);
+    if (bytes > 40 * 1024) return cudaErrorInvalidValue;
+    dim3 grid(tokens, (heads + kWarps - 1) / kWarps);
+#define TAU_ATTEND(T)                                                                                                                         \
+    tau_launch(masked_attention_kernel<T>, grid, dim3(kWarps * 32), bytes, s, static_cast<const T*>(queries), static_cast<const T*>(rows), static_cast<T*>(out), \
+               out_stride, positions, token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale)
+    if (dtype == TAU_F32) TAU_ATTEND(float);
+    else if (dtype == TAU_BF16) TAU_ATTEND(bf16);
+    else return cudaErrorInvalidValue;
+#undef TAU_ATTEND
+    return tau_launch_status();
+}

@@ -189,8 +189,8 @@ moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router,
 // grid (token-place pairs, feature tiles).  gate_up: [experts, 2 * inner, width], gate rows first.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
-moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, const int* __restrict__ chosen, T* __restrict__ inner_out,
-                   int width, int inner, int top, int features_per_block, int interleave) {
+moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, const int* __restrict__ chosen, const float* __restrict__ input_weights,
+                   T* __restrict__ inner_out, int width, int inner, int top, int features_per_block, int interleave) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ __align__(16) float row[];
@@ -198,6 +198,8 @@ moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, 
     for (int column = threadIdx.x; column < width; column += blockDim.x) row[column] = to_float(hidden[static_cast<size_t>(token) * width + column]);
     __syncthreads();
     const T* weights = gate_up + static_cast<size_t>(chosen[pair]) * 2 * inner * width;
+    // A weight on the expert's input: both products are linear in the row, so the weight multiplies their 32-bit sums.
+    const float input_weight = input_weights ? input_weights[pair] : 1.0f;
     const int begin = blockIdx.y * features_per_block, end = min(inner, begin + features_per_block);
     for (int feature = begin + warp; feature < end; feature += kWarps) {
         // Plain: gate rows, then up rows.  Interleaved: groups of `interleave` gate rows, each followed by its up rows.
@@ -205,6 +207,8 @@ moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, 
         const int up_row = interleave ? gate_row + interleave : inner + feature;
         float gate, up;
         warp_dot_pair(weights + static_cast<size_t>(gate_row) * width, row, weights + static_cast<size_t>(up_row) * width, row, width, lane, gate, up);
+        gate *= input_weight;
+        up *= input_weight;
         if (lane == 0) inner_out[static_cast<size_t>(pair) * inner + feature] = from_float<T>(gate / (1.0f + expf(-gate)) * up);
     }
 }
@@ -230,12 +234,12 @@ moe_down_kernel(const T* __restrict__ inner_in, const T* __restrict__ down, cons
             const T* second = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place + 1]) * width + feature) * inner;
             float a, b;
             warp_dot_pair(first, rows + place * inner, second, rows + (place + 1) * inner, inner, lane, a, b);
-            sum = fmaf(weights[static_cast<size_t>(token) * top + place], a, sum);
-            sum = fmaf(weights[static_cast<size_t>(token) * top + place + 1], b, sum);
+            sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, a, sum);
+            sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place + 1] : 1.0f, b, sum);
         }
         if (place < top) {
             const T* weight_row = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place]) * width + feature) * inner;
-            sum = fmaf(weights[static_cast<size_t>(token) * top + place], warp_dot(weight_row, rows + place * inner, inner, lane), sum);
+            sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, warp_dot(weight_row, rows + place * inner, inner, lane), sum);
         }
         if (lane == 0) {
             if (shared_out) sum += (shared_gate ? shared_gate[token] : 1.0f) * to_float(shared_out[static_cast<size_t>(token) * width + feature]);
@@ -273,14 +277,21 @@ moe_sort_kernel(const int* __restrict__ chosen, int pairs, int experts, int* __r
     }
 }
 
-// gathered[i] = hidden[order[i] / top]: the rows of each expert's tokens side by side.
+// gathered[i] = hidden[order[i] / top] (times input_weights[order[i]], if given): the rows of each expert's tokens side by side.
 template <typename T>
-__global__ void moe_gather_kernel(const T* __restrict__ hidden, const int* __restrict__ order, T* __restrict__ gathered, int width, int top) {
+__global__ void moe_gather_kernel(const T* __restrict__ hidden, const int* __restrict__ order, const float* __restrict__ input_weights, T* __restrict__ gathered,
+                                  int width, int top) {
     grid_dependents_launch();
     grid_dependency_wait();
-    const T* source = hidden + static_cast<size_t>(order[blockIdx.x] / top) * width;
+    const int pair = order[blockIdx.x];
+    const T* source = hidden + static_cast<size_t>(pair / top) * width;
     T* target = gathered + static_cast<size_t>(blockIdx.x) * width;
-    for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = source[column];
+    if (input_weights) {
+        const float weight = input_weights[pair];
+        for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = from_float<T>(weight * to_float(source[column]));
+    } else {
+        for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = source[column];
+    }
 }
 
 // out[token] = sum over places of weight * rows[position[token, place]] + shared_gate * shared[token], in place order.
@@ -293,7 +304,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __
     for (int column = threadIdx.x; column < width; column += blockDim.x) {
         float sum = 0.0f;
         for (int place = 0; place < top; ++place)
-            sum = fmaf(weights[static_cast<size_t>(token) * top + place], rows[static_cast<size_t>(position[static_cast<size_t>(token) * top + place]) * width + column], sum);
+            sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, rows[static_cast<size_t>(position[static_cast<size_t>(token) * top + place]) * width + column], sum);
         if (shared_out) sum += (shared_gate ? shared_gate[token] : 1.0f) * to_float(shared_out[static_cast<size_t>(token) * width + column]);
         out[static_cast<size_t>(token) * width + column] = sum;
     }
@@ -314,7 +325,7 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
         if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
             return cudaErrorInvalidValue;
         tau_launch(moe_gate_up_kernel<T>, dim3(tokens * top, (inner + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a),
-                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<T*>(o1), width, inner, top, per_block, flag_a);
+                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<const float*>(d), static_cast<T*>(o1), width, inner, top, per_block, flag_a);
     } else {
         const int per_block = tokens * ((width + 63) / 64) >= 1024 ? 64 : tokens * ((width + 31) / 32) >= 1024 ? 32 : 16;   // few tokens: smaller tiles, more blocks
         const size_t bytes = static_cast<size_t>(top) * inner * sizeof(float);
@@ -340,20 +351,20 @@ TAU_EXPORT int tau_moe_route(int dtype, const void* hidden, const float* router,
     return cudaErrorInvalidValue;
 }
 
-TAU_EXPORT int tau_moe_gate_up(int dtype, const void* hidden, const void* gate_up, const int* chosen, void* inner_out, int tokens, int width, int inner,
-                               int top, int interleave, void* stream) {
+TAU_EXPORT int tau_moe_gate_up(int dtype, const void* hidden, const void* gate_up, const int* chosen, const float* input_weights, void* inner_out, int tokens,
+                               int width, int inner, int top, int interleave, void* stream) {
     if (tokens <= 0) return 0;
     if (!hidden || !gate_up || !chosen || !inner_out || width <= 0 || inner <= 0 || top <= 0 || static_cast<long long>(tokens) * top > 0x7fffffff) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
-    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, nullptr, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
+    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, input_weights, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, input_weights, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
     return cudaErrorInvalidValue;
 }
 
 TAU_EXPORT int tau_moe_down(int dtype, const void* inner_in, const void* down, const int* chosen, const float* weights, const void* shared_out,
                             const float* shared_gate, float* out, int tokens, int width, int inner, int top, void* stream) {
     if (tokens <= 0) return 0;
-    if (!inner_in || !down || !chosen || !weights || !out || width <= 0 || inner <= 0 || top <= 0) return cudaErrorInvalidValue;
+    if (!inner_in || !down || !chosen || !out || width <= 0 || inner <= 0 || top <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == TAU_F32) return launch_all<float>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
     if (dtype == TAU_BF16) return launch_all<bf16>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
@@ -368,12 +379,13 @@ TAU_EXPORT int tau_moe_sort(const int* chosen, int pairs, int experts, int* offs
     return tau_launch_status();
 }
 
-TAU_EXPORT int tau_moe_gather(int dtype, const void* hidden, const int* order, void* gathered, int pairs, int width, int top, void* stream) {
+TAU_EXPORT int tau_moe_gather(int dtype, const void* hidden, const int* order, const float* input_weights, void* gathered, int pairs, int width, int top,
+                              void* stream) {
     if (pairs <= 0) return 0;
     if (!hidden || !order || !gathered || width <= 0 || top <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) tau_launch(moe_gather_kernel<float>, dim3(pairs), dim3(kThreads), 0, s, static_cast<const float*>(hidden), order, static_cast<float*>(gathered), width, top);
-    else if (dtype == TAU_BF16) tau_launch(moe_gather_kernel<bf16>, dim3(pairs), dim3(kThreads), 0, s, static_cast<const bf16*>(hidden), order, static_cast<bf16*>(gathered), width, top);
+    if (dtype == TAU_F32) tau_launch(moe_gather_kernel<float>, dim3(pairs), dim3(kThreads), 0, s, static_cast<const float*>(hidden), order, input_weights, static_cast<float*>(gathered), width, top);
+    else if (dtype == TAU_BF16) tau_launch(moe_gather_kernel<bf16>, dim3(pairs), dim3(kThreads), 0, s, static_cast<const bf16*>(hidden), order, input_weights, static_cast<bf16*>(gathered), width, top);
     else return cudaErrorInvalidValue;
     return tau_launch_status();
 }
@@ -381,7 +393,7 @@ TAU_EXPORT int tau_moe_gather(int dtype, const void* hidden, const int* order, v
 TAU_EXPORT int tau_moe_combine(int dtype, const float* rows, const int* position, const float* weights, const void* shared_out, const float* shared_gate,
                                float* out, int tokens, int width, int top, void* stream) {
     if (tokens <= 0) return 0;
-    if (!rows || !position || !weights || !out || width <= 0 || top <= 0) return cudaErrorInvalidValue;
+    if (!rows || !position || !out || width <= 0 || top <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (dtype == TAU_F32) tau_launch(moe_combine_kernel<float>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const float*>(shared_out), shared_gate, out, width, top);
     else if (dtype == TAU_BF16) tau_launch(moe_combine_kernel<bf16>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const bf16*>(shared_out), shared_gate, out, width, top);

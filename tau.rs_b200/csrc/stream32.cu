@@ -12,7 +12,7 @@ __device__ __forceinline__ float load_as_float(const void* base, int code, size_
 }
 
 template <typename T>
-__global__ void embedding_f32_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out, int width, int vocab) {
+__global__ void embedding_f32_kernel(const int* __restrict__ tokens, const T* __restrict__ table, float* __restrict__ out, int width, int vocab, float scale) {
     grid_dependents_launch();
     grid_dependency_wait();
     const int row = blockIdx.x;
@@ -20,7 +20,7 @@ __global__ void embedding_f32_kernel(const int* __restrict__ tokens, const T* __
     float* target = out + static_cast<size_t>(row) * width;
     const bool inside = token >= 0 && token < vocab;   // refused on the host already; never read outside the table
     const T* source = table + static_cast<size_t>(inside ? token : 0) * width;
-    for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = inside ? to_float(source[column]) : 0.0f;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = inside ? to_float(source[column]) * scale : 0.0f;
 }
 
 // r = rows ? rows[i] : i.  sum = stream[r] + (a[r] + b[r]) in 32-bit; if `update` the sum replaces stream[r];
@@ -59,11 +59,12 @@ stream_add_norm_kernel(float* __restrict__ stream, const void* __restrict__ a, i
 }
 
 // values [rows, groups * group_width] in 32-bit.  With `normalize` each group of a row is divided by its root mean square;
-// then times weight (if any), times sigmoid(gate) (if any; gate rows lie `gate_stride` apart), rounded once to T.
+// then times weight (if any), times sigmoid(gate) or, with `silu_gate`, gate * sigmoid(gate) (if any; gate rows lie `gate_stride`
+// apart), rounded once to T; output rows lie `out_stride` apart.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 gated_group_norm_kernel(const float* __restrict__ values, const float* __restrict__ weight, const T* __restrict__ gate, long long gate_stride,
-                        T* __restrict__ out, int groups, int group_width, float eps, int normalize) {
+                        T* __restrict__ out, long long out_stride, int groups, int group_width, float eps, int normalize, int silu_gate) {
     grid_dependents_launch();
     grid_dependency_wait();
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
@@ -85,8 +86,11 @@ gated_group_norm_kernel(const float* __restrict__ values, const float* __restric
                 const int index = group * group_width + column;
                 float value = source[index] * inverse;
                 if (weight) value *= weight[index];
-                if (gate) value *= 1.0f / (1.0f + expf(-to_float(gate[static_cast<size_t>(row) * gate_stride + index])));
-                out[static_cast<size_t>(row) * width + index] = from_float<T>(value);
+                if (gate) {
+                    const float z = to_float(gate[static_cast<size_t>(row) * gate_stride + index]);
+                    value *= (silu_gate ? z : 1.0f) / (1.0f + expf(-z));
+                }
+                out[static_cast<size_t>(row) * out_stride + index] = from_float<T>(value);
             }
         }
         return;
@@ -105,20 +109,23 @@ gated_group_norm_kernel(const float* __restrict__ values, const float* __restric
             const int index = group * group_width + column;
             float value = source[index] * inverse;
             if (weight) value *= weight[index];
-            if (gate) value *= 1.0f / (1.0f + expf(-to_float(gate[static_cast<size_t>(row) * gate_stride + index])));
-            out[static_cast<size_t>(row) * width + index] = from_float<T>(value);
+            if (gate) {
+                const float z = to_float(gate[static_cast<size_t>(row) * gate_stride + index]);
+                value *= (silu_gate ? z : 1.0f) / (1.0f + expf(-z));
+            }
+            out[static_cast<size_t>(row) * out_stride + index] = from_float<T>(value);
         }
     }
 }
 
 }  // namespace
 
-TAU_EXPORT int tau_embedding_f32(int table_dtype, const int* tokens, const void* table, float* out, int rows, int width, int vocab, void* stream) {
+TAU_EXPORT int tau_embedding_f32(int table_dtype, const int* tokens, const void* table, float* out, int rows, int width, int vocab, float scale, void* stream) {
     if (rows <= 0) return 0;
     if (!tokens || !table || !out || width <= 0 || vocab <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (table_dtype == TAU_F32) tau_launch(embedding_f32_kernel<float>, dim3(rows), dim3(kThreads), 0, s, tokens, static_cast<const float*>(table), out, width, vocab);
-    else if (table_dtype == TAU_BF16) tau_launch(embedding_f32_kernel<bf16>, dim3(rows), dim3(kThreads), 0, s, tokens, static_cast<const bf16*>(table), out, width, vocab);
+    if (table_dtype == TAU_F32) tau_launch(embedding_f32_kernel<float>, dim3(rows), dim3(kThreads), 0, s, tokens, static_cast<const float*>(table), out, width, vocab, scale);
+    else if (table_dtype == TAU_BF16) tau_launch(embedding_f32_kernel<bf16>, dim3(rows), dim3(kThreads), 0, s, tokens, static_cast<const bf16*>(table), out, width, vocab, scale);
     else return cudaErrorInvalidValue;
     return tau_launch_status();
 }
@@ -134,14 +141,14 @@ TAU_EXPORT int tau_stream_add_norm(int out_dtype, float* stream_values, const vo
     return tau_launch_status();
 }
 
-TAU_EXPORT int tau_gated_group_norm(int dtype, const float* values, const float* weight, const void* gate, long long gate_stride, void* out, int rows,
-                                    int groups, int group_width, float eps, int normalize, void* stream) {
+TAU_EXPORT int tau_gated_group_norm(int dtype, const float* values, const float* weight, const void* gate, long long gate_stride, void* out, long long out_stride,
+                                    int rows, int groups, int group_width, float eps, int normalize, int silu_gate, void* stream) {
     if (rows <= 0) return 0;
     if (!values || !out || groups <= 0 || group_width <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int threads = 256;
-    if (dtype == TAU_F32) tau_launch(gated_group_norm_kernel<float>, dim3(rows), dim3(threads), 0, s, values, weight, static_cast<const float*>(gate), gate_stride, static_cast<float*>(out), groups, group_width, eps, normalize);
-    else if (dtype == TAU_BF16) tau_launch(gated_group_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, values, weight, static_cast<const bf16*>(gate), gate_stride, static_cast<bf16*>(out), groups, group_width, eps, normalize);
+    if (dtype == TAU_F32) tau_launch(gated_group_norm_kernel<float>, dim3(rows), dim3(threads), 0, s, values, weight, static_cast<const float*>(gate), gate_stride, static_cast<float*>(out), out_stride, groups, group_width, eps, normalize, silu_gate);
+    else if (dtype == TAU_BF16) tau_launch(gated_group_norm_kernel<bf16>, dim3(rows), dim3(threads), 0, s, values, weight, static_cast<const bf16*>(gate), gate_stride, static_cast<bf16*>(out), out_stride, groups, group_width, eps, normalize, silu_gate);
     else return cudaErrorInvalidValue;
     return tau_launch_status();
 }

@@ -22,7 +22,9 @@ class CacheNeed:
     `kind == "kv"`: keys and values of `n_kv_heads` heads of `head_dim` elements for
     every position (or for the last `window` positions).  `kind == "rows"`: one row of
     `row_width` elements for every position (or for the last `window`), paged like keys
-    and values (a latent that keys and values are expanded from, say).  `kind == "state"`:
+    and values (a latent that keys and values are expanded from, say).  With `chunk` a
+    query reads only the positions of its own chunk of `chunk` positions (chunks counted from
+    position 0), so that what lies before the newest chunk need not be kept.  `kind == "state"`:
     one tensor of `state_shape` and `state_dtype` for each sequence, zero when the sequence
     starts, whatever its length.
     """
@@ -34,6 +36,7 @@ class CacheNeed:
     state_shape: Tuple[int, ...] = ()
     state_dtype: torch.dtype = torch.float32
     row_width: int = 0
+    chunk: Optional[int] = None
 
 
 class Part:
@@ -80,6 +83,11 @@ class Mixer(Part):
         context of a decode step at all (None: it does not).  The number of splits is chosen so that all blocks of a step
         are resident at once, and it is part of a captured graph's key."""
         return None
+
+    def extra_cache_needs(self) -> Dict[str, CacheNeed]:
+        """What the mixer keeps for a sequence beside `cache_need()`, by role (the tail of inputs of a convolution, say); `forward`
+        finds the views under `cache.extra[role]`.  The block hands the roles on (`Block.extra_cache_needs`)."""
+        return {}
 
     def forward(self, hidden, step, cache, writes_cache: bool):
         raise NotImplementedError

@@ -266,3 +266,96 @@ class SublayerNormBlock(Block):
         out = torch.empty(shape, dtype=torch.float32, device=device)
         kernels.unit_add_mix(x, y, self.side_norm, 0.0 if y is None else spec.token_side.eps, x, step.results, self.mix, out)
         return out, None
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """A norm before and a norm behind each sublayer, on a 32-bit residual stream `x`:
+
+        x <- x + s1 * post1(mixer(pre1(x)))
+        x <- x + s2 * post2(feed_forward(pre2(x)))          (if there is a feed-forward)
+
+    `s1`, `s2` are vectors of the stream's width (`layer_scale`); because the norms behind the sublayers have a weight and no bias,
+    each is multiplied into its norm's weight once, when the weights are loaded.  A sublayer's result is normalised, added to the
+    stream and the new stream normalised for the next reader by one kernel where the next reader is this block's own feed-forward.
+    Weight names under the prefix: `norm1`, `norm1b`, `norm2`, `norm2b`, `ls1`, `ls2`, `mix.*`, `mlp.*`.
+    """
+
+    mixer_name = "mix"
+    feed_forward_name = "mlp"
+    norm_names = ("norm1", "norm1b", "norm2", "norm2b")
+    scale_names = ("ls1", "ls2")
+
+    def __init__(self, spec, dtype, device):
+        from ..weights.tensor_spec import TensorSpec
+
+        self.spec, self.dtype = spec, dtype
+        prefix = spec.prefix
+        self.width = spec.mixer_norm.width
+        pre1, post1, pre2, post2 = (f"{prefix}.{name}" for name in self.norm_names)
+        self.mixer_norm = build("norm", spec.mixer_norm, name=pre1, dtype=dtype, device=device)
+        self.mixer_post_norm = build("norm", spec.mixer_post_norm, name=post1, dtype=dtype, device=device)
+        self.mixer = build("mixer", spec.mixer, prefix=f"{prefix}.{self.mixer_name}", dtype=dtype, device=device)
+        self.feed_forward = self.feed_forward_norm = self.feed_forward_post_norm = None
+        if spec.feed_forward is not None:
+            self.feed_forward = build("feed_forward", spec.feed_forward, prefix=f"{prefix}.{self.feed_forward_name}", dtype=dtype, device=device)
+            self.feed_forward_norm = build("norm", spec.feed_forward_norm, name=pre2, dtype=dtype, device=device)
+            self.feed_forward_post_norm = build("norm", spec.feed_forward_post_norm, name=post2, dtype=dtype, device=device)
+        for norm in (spec.mixer_norm, spec.mixer_post_norm, spec.feed_forward_norm, spec.feed_forward_post_norm):
+            if norm is None:
+                continue
+            if norm.kind not in ("layer_norm", "rms_norm"):
+                raise ValueError(f"the block's kernels compute layer_norm and rms_norm; a norm of kind {norm.kind!r} is not served")
+            if getattr(norm, "bias", True) and norm.kind == "layer_norm":
+                raise ValueError("the block's norms have a weight and no bias")
+        self._own = {}
+        if spec.layer_scale:
+            self._own[f"{prefix}.{self.scale_names[0]}"] = TensorSpec((self.width,), role="vector", init="ones")
+            if self.feed_forward is not None:
+                self._own[f"{prefix}.{self.scale_names[1]}"] = TensorSpec((self.width,), role="vector", init="ones")
+        self._held = {}
+        self.mixer_post_weight = self.feed_forward_post_weight = None
+        self._children = tuple(part for part in (self.mixer_norm, self.mixer_post_norm, self.mixer, self.feed_forward_norm, self.feed_forward_post_norm,
+                                                 self.feed_forward) if part is not None)
+        self.capturable = all(getattr(part, "capturable", True) for part in self._children)
+
+    cache_need = PreNormBlock.cache_need
+    decode_blocks = PreNormBlock.decode_blocks
+    tensor_specs = SublayerNormBlock.tensor_specs
+    assign = SublayerNormBlock.assign
+
+    def extra_cache_needs(self):
+        return self.mixer.extra_cache_needs()
+
+    def finalize_weights(self):
+        prefix, spec = self.spec.prefix, self.spec
+        for part in self._children:
+            part.finalize_weights()
+        self.mixer_post_weight = self.mixer_post_norm.weight
+        self.feed_forward_post_weight = None if self.feed_forward is None else self.feed_forward_post_norm.weight
+        if spec.layer_scale:
+            self.mixer_post_weight = (self.mixer_post_weight * self._held.pop(f"{prefix}.{self.scale_names[0]}")).contiguous()
+            if self.feed_forward is not None:
+                self.feed_forward_post_weight = (self.feed_forward_post_weight * self._held.pop(f"{prefix}.{self.scale_names[1]}")).contiguous()
+
+    def bytes_read_per_step(self, dtype) -> int:
+        own = sum(4 * math.prod(spec.shape) for spec in self._own.values())
+        return own + sum(part.bytes_read_per_step(dtype) for part in self._children)
+
+    def forward(self, residual, branch, step, cache, writes_cache: bool):
+        spec = self.spec
+        if branch is not None:
+            raise ValueError("this block reads a finished stream; the block before it must not leave a branch pending")
+        if residual.dtype != torch.float32:
+            raise ValueError("this block keeps its residual stream in 32-bit (ModelSpec.residual_dtype)")
+        x = residual
+        mixed = self.mixer.forward(self.mixer_norm.forward(x), step, cache, writes_cache)
+        centred = spec.mixer_post_norm.kind == "layer_norm"
+        if self.feed_forward is None:
+            kernels.gated_add_norm(x, x, mixed, None, self.mixer_post_weight, None, spec.mixer_post_norm.eps, centred)
+            return x, None
+        kernels.gated_add_norm(x, x, mixed, None, self.mixer_post_weight, None, spec.mixer_post_norm.eps, centred)
+        fed = self.feed_forward.forward(self.feed_forward_norm.forward(x), step)
+        kernels.gated_add_norm(x, x, fed, None, self.feed_forward_post_weight, None, spec.feed_forward_post_norm.eps,
+                               spec.feed_forward_post_norm.kind == "layer_norm")
+        return x, None

@@ -1,4 +1,4 @@
-"""SwiGLU feed-forward: `down(silu(gate(x)) * up(x))`, no biases.
+"""Gated feed-forward: `down(act(gate(x)) * up(x))`, no biases; `act` is SiLU (SwiGLU) or, by the spec's `activation`, ReLU.
 
 crates/models/src/components/mlp.rs:99-122,177-191; gate and up are one stacked product
 followed by one fused activation kernel (crates/models/src/components/mlp/
@@ -19,9 +19,12 @@ from .registry import register_feed_forward
 class SwiGLU(FeedForward):
     def __init__(self, spec, prefix: str, dtype, device):
         self.spec = spec
-        # Where the gated product exists (bfloat16, aligned sizes) gate and up rows are interleaved for it and the
-        # activation is its epilogue; otherwise the two are stacked and the activation is a kernel of its own.
-        self.fused = kernels.gated_fits(spec.hidden, spec.intermediate, dtype)
+        self.activation = getattr(spec, "activation", "silu")
+        if self.activation not in ("silu", "relu"):
+            raise ValueError(f"unknown activation {self.activation!r}")
+        # Where the gated product exists (bfloat16, aligned sizes; its epilogue is SiLU) gate and up rows are interleaved for it and
+        # the activation is its epilogue; otherwise the two are stacked and the activation is a kernel of its own.
+        self.fused = self.activation == "silu" and kernels.gated_fits(spec.hidden, spec.intermediate, dtype)
         gate, up, down = (getattr(spec, key, default) for key, default in (("gate_name", "gate_proj"), ("up_name", "up_proj"), ("down_name", "down_proj")))
         suffix = getattr(spec, "weight_suffix", ".weight")
         self.gate_up = StackedLinear(
@@ -46,7 +49,7 @@ class SwiGLU(FeedForward):
             return self.down.forward(self.gate_up.forward_gated(hidden))
         stacked = self.gate_up.forward(hidden)
         activated = torch.empty((hidden.shape[0], self.spec.intermediate), dtype=hidden.dtype, device=hidden.device)
-        kernels.silu_mul(stacked, activated)
+        kernels.silu_mul(stacked, activated, relu=self.activation == "relu")
         return self.down.forward(activated)
 
 

@@ -143,7 +143,7 @@ class DecoderModel:
             residual = step.results[0]
         else:
             residual = torch.empty((step.n_tokens, spec.hidden), dtype=self.residual_dtype, device=self.device)
-        kernels.embedding(step.token_ids, self.embedding, residual)
+        kernels.embedding(step.token_ids, self.embedding, residual, getattr(spec, "embedding_scale", 1.0))
         if self.input_position is not None:
             self.input_position.add_to(residual, step)
         branch = None

@@ -54,12 +54,15 @@ class LayerNorm(Norm):
 
     def tensor_specs(self):
         width = self.spec.width
-        return {self.name: TensorSpec((width,), role="vector", init="ones"), self.bias_name: TensorSpec((width,), role="vector")}
+        specs = {self.name: TensorSpec((width,), role="vector", init="ones")}
+        if getattr(self.spec, "bias", True):
+            specs[self.bias_name] = TensorSpec((width,), role="vector")
+        return specs
 
     def assign(self, name, tensor):
         if name == self.name:
             self.weight = tensor
-        elif name == self.bias_name:
+        elif name == self.bias_name and getattr(self.spec, "bias", True):
             self.bias = tensor
         else:
             raise KeyError(name)

@@ -3,6 +3,7 @@
     z = W_router h (+ b_router) (32-bit);   s = sigmoid(z) (or softmax(z))
     chosen = the `top` experts with the largest s + correction;   weights = s of the chosen (renormalised only if asked)
     out = sum over chosen e of weight_e * W_down,e (silu(W_gate,e h) * (W_up,e h))  +  sigmoid(w_sg . h) * shared(h)
+    (`weigh == "input"`: the weight multiplies what the expert reads instead, out = sum over chosen e of expert_e(weight_e * h))
 
 The router, the choice and the weighted sum are 32-bit, and so is the output.  The experts' weights are stacked
 (`[experts, 2 I, width]`, `[experts, width, I]`).  Two ways through the experts:
@@ -38,6 +39,8 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"unknown router score {spec.score!r}")
         if not 1 <= spec.top <= spec.experts:
             raise ValueError("top must lie between 1 and the number of experts")
+        if getattr(spec, "weigh", "output") not in ("output", "input"):
+            raise ValueError(f"the experts' weights act on their output or their input, not on {spec.weigh!r}")
         if spec.shared_gate and spec.shared is None:
             raise ValueError("a shared gate needs a shared expert")
         self.spec, self.prefix, self.dtype = spec, prefix, dtype
@@ -112,8 +115,9 @@ class RoutedExperts(FeedForward):
             self._grouped(hidden, chosen, weights, shared_out, shared_gate, out)
             return out
         inner = torch.empty((tokens, spec.top, spec.intermediate), dtype=hidden.dtype, device=device)
-        kernels.moe_gate_up(hidden, self.gate_up, chosen, inner, self.interleave)
-        kernels.moe_down(inner, self.down, chosen, weights, shared_out, shared_gate, out)
+        on_input = getattr(spec, "weigh", "output") == "input"
+        kernels.moe_gate_up(hidden, self.gate_up, chosen, inner, self.interleave, weights if on_input else None)
+        kernels.moe_down(inner, self.down, chosen, None if on_input else weights, shared_out, shared_gate, out)
         return out
 
     def _grouped(self, hidden, chosen, weights, shared_out, shared_gate, out) -> None:
@@ -125,9 +129,10 @@ class RoutedExperts(FeedForward):
         kernels.moe_sort(chosen, spec.experts, offsets, order, position)
         bounds = offsets.tolist()                        # the host waits here for the router
         gathered = torch.empty((pairs, spec.hidden), dtype=hidden.dtype, device=device)
-        kernels.moe_gather(hidden, order, spec.top, gathered)
+        on_input = getattr(spec, "weigh", "output") == "input"
+        kernels.moe_gather(hidden, order, spec.top, gathered, weights if on_input else None)
         inner = torch.empty((pairs, spec.intermediate), dtype=hidden.dtype, device=device)
         rows = torch.empty((pairs, spec.hidden), dtype=torch.float32, device=device)
         kernels.gemm_tc_groups(gathered, self.gate_up, inner, bounds, gated=True)
         kernels.gemm_tc_groups(inner, self.down, rows, bounds)
-        kernels.moe_combine(rows, position, weights, shared_out, shared_gate, out)
+        kernels.moe_combine(rows, position, None if on_input else weights, shared_out, shared_gate, out)
