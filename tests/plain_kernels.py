@@ -18,8 +18,8 @@ def _wide(tensor):
     return tensor.to(torch.float32)
 
 
-def embedding(tokens, table, out):
-    out.copy_(table[tokens.long()])
+def embedding(tokens, table, out, scale=1.0):
+    out.copy_(table[tokens.long()] * scale)
 
 
 def rms_norm(values, weight, eps, out, rows=None, branch=None):
@@ -37,10 +37,11 @@ def add_rms_norm(branch, residual, weight, eps, out):
     rms_norm(residual, weight, eps, out)
 
 
-def silu_mul(stacked, out):
+def silu_mul(stacked, out, relu=False):
     width = out.shape[-1]
     gate, up = _wide(stacked[:, :width]), _wide(stacked[:, width:])
-    out.copy_((gate / (1.0 + torch.exp(-gate)) * up).to(out.dtype))
+    activated = torch.clamp(gate, min=0.0) if relu else gate / (1.0 + torch.exp(-gate))
+    out.copy_((activated * up).to(out.dtype))
 
 
 def linear(values, weight, bias, out):
