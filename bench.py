@@ -313,9 +313,35 @@ def bisudra_sizes():
     }
 
 
+def pegurax_sizes():
+    """Layer sizes that resemble a real model of Pegurax's kind: layers whose mixer is a chunked softmax attention (128-element heads, 8
+    key/value heads, chunks of 1,024 positions) beside a gated delta rule (128 by 128 states, half as many key heads as heads, 4 taps)
+    alternate with selective scans (twice the width inside, 16 states per channel, 4 taps); the feed-forwards are dense, four times the
+    width, or 32 experts of which 4 are chosen.  Beside it the closest design that was here before, Fasesun (attention, matrix-state
+    recurrences and routed experts as well), and a dense Qwen3, each of the same width, depth and vocabulary."""
+    def pegurax(width, heads, expert_ff):
+        left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+                "rot": {"base": 10000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+        right = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}
+        parallel = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
+        scan = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
+        dense, routed = {"kind": "dense", "ff": 4 * width}, {"kind": "moe", "router": {"experts": 32, "top": 4}, "expert": {"ff": expert_ff}}
+        layers = [{"type": "parallel", "mixer": parallel, "mlp": dense}, {"type": "mamba1", "mixer": scan, "mlp": routed},
+                  {"type": "parallel", "mixer": parallel, "mlp": routed}, {"type": "mamba1", "mixer": scan, "mlp": dense}]
+        return {"architecture": "Pegurax", "embedding": {"scale": 1.0}, "layers": layers, "norm": {"eps": 1e-5}, "vocab": 32768, "width": width}
+
+    fasesun, dense = fasesun_sizes(), bisudra_sizes()
+    return {
+        "1024": (pegurax(1024, 8, 704), dense["1024"][1], fasesun["1024"][0]),
+        "2048": (pegurax(2048, 16, 1344), dense["2048"][1], fasesun["2048"][0]),
+        "4096": (pegurax(4096, 32, 2752), dense["4096"][1], fasesun["4096"][0]),
+    }
+
+
 def design_comparison(args) -> int:
-    """`--design fasesun|bisudra`: prefill and decode throughput of the design's layers at three real sizes beside a dense Qwen3 of equal
-    width, depth and active feed-forward width, with the device time of each kernel class in one prompt step and one decode step."""
+    """`--design fasesun|bisudra|pegurax`: prefill and decode throughput of the design's layers at three real sizes beside a dense Qwen3
+    of equal width, depth and active feed-forward width (Pegurax also beside Fasesun), with the device time of each kernel class in one
+    prompt step and one decode step."""
     import numpy as np
     import torch
 
@@ -330,10 +356,12 @@ def design_comparison(args) -> int:
     records = []
     clocks = ClockSampler()
     clocks.start()
-    sizes = bisudra_sizes() if args.design == "bisudra" else fasesun_sizes()
-    for size, (design_config, dense_config) in sizes.items():
+    sizes = {"bisudra": bisudra_sizes, "fasesun": fasesun_sizes, "pegurax": pegurax_sizes}[args.design]()
+    for size, (design_config, dense_config, *others) in sizes.items():
+        if args.widths and size not in args.widths.split(","):
+            continue
         record = {"size": size, "batch": batch, "context": context}
-        for label, config in ((args.design, design_config), ("qwen3", dense_config)):
+        for label, config in ((args.design, design_config), ("qwen3", dense_config), *((other["architecture"].lower(), other) for other in others)):
             model = tau_rs_b200.random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
             vocab = model.spec.vocab_size
             engine = Engine(model, max_tokens=batch * (context + 256), max_sequence_tokens=context + 256)
@@ -347,12 +375,12 @@ def design_comparison(args) -> int:
                 torch.cuda.synchronize()
                 return start.elapsed_time(stop)
 
-            def prefill_once(classes=False):
+            def prefill_once(classes=False, by_name=False):
                 slot = engine.open_sequence()
                 tokens = rng.integers(0, vocab, size=context).tolist()
                 if classes:
                     torch.cuda.synchronize()
-                    kernels.start_timing()
+                    kernels.start_timing(by_name)
                 engine.step([StepEntry(slot, tokens, [context - 1])])
                 per_class = kernels.take_timing(stop=True) if classes else None
                 engine.close_sequence(slot)
@@ -362,6 +390,7 @@ def design_comparison(args) -> int:
                 prefill_once()
             prefill_ms = min(timed(prefill_once) for _ in range(3))
             prefill_classes = prefill_once(classes=True)
+            prefill_names = prefill_once(classes=True, by_name=True)
             slots = [engine.open_sequence() for _ in range(batch)]
             engine.step([StepEntry(slot, rng.integers(0, vocab, size=context).tolist(), []) for slot in slots])
 
@@ -379,6 +408,9 @@ def design_comparison(args) -> int:
             kernels.start_timing()
             decode_once()
             decode_classes = kernels.take_timing(stop=True)
+            kernels.start_timing(True)
+            decode_once()
+            decode_names = kernels.take_timing(stop=True)
             read = engine.bytes_read_by_a_decode_step()
             if label != "qwen3":
                 # `bytes_read_by_a_decode_step` counts the experts that one token chooses; a batch whose tokens choose independently
@@ -394,6 +426,7 @@ def design_comparison(args) -> int:
                 "decode_tok_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
                 "decode_bytes_per_step": read, "decode_frac_of_copy_bandwidth": round(read / (decode_ms * 1e-3) / (peaks["hbm_gbs"] * 1e9), 4),
                 "prefill_ms_by_class": prefill_classes, "decode_ms_by_class": decode_classes,
+                "prefill_ms_by_kernel": prefill_names, "decode_ms_by_kernel": decode_names,
             }
             for slot in slots:
                 engine.close_sequence(slot)
@@ -420,7 +453,8 @@ def main() -> int:
     parser.add_argument("--sections", default="prefill,decode,points,e2e",
                         help="which measurements to run: prefill, decode, points, e2e, kernels (the counterparts of the reference arm's kernels), "
                              "classes (time per kernel class of a decode step, outside a graph)")
-    parser.add_argument("--design", default="", choices=["", "fasesun", "bisudra"],
+    parser.add_argument("--widths", default="", help="with --design: only these of the widths 1024, 2048, 4096 (comma-separated)")
+    parser.add_argument("--design", default="", choices=["", "fasesun", "bisudra", "pegurax"],
                         help="instead of the default workload: layers of this design at real sizes beside a dense Qwen3 of equal size")
     args = parser.parse_args()
 

@@ -192,7 +192,7 @@ class ScaledRotationSpec:
 @dataclass(frozen=True)
 class MaskedAttentionSpec:
     """Grouped-query softmax attention whose keys (`dim`) and values (`value_dim`) may differ in size, over one cached row per
-    position.  `qk_norm == "projection"`: queries, and keys, pass an RMS norm over their whole projection (all heads at once) with a
+    position (or over pages of ordinary heads where the sizes allow the tensor-core kernel).  `qk_norm == "projection"`: queries, and keys, pass an RMS norm over their whole projection (all heads at once) with a
     weight of that size, before `position`.  A query at position i sees key j <= i within `window` positions, or (with `chunk`)
     only if floor(j / chunk) == floor(i / chunk), chunks counted from position 0.  `sink`: one is added to the softmax's
     denominator (a key with score 0 and no value).  `out_scale` multiplies what the output projection reads."""

@@ -5,7 +5,8 @@
 // head, whose keys are walked in tiles of 64 (one cache page), with both accumulators in tensor memory:
 //
 //   S = Q K^T     tcgen05.mma, A = Q tile and B = key tile from shared memory (both K-major, 128-byte swizzle, by TMA)
-//   softmax       four warps, one query row per thread: tcgen05.ld of the row, mask (`key <= query position`,
+//   softmax       four warps, one query row per thread: tcgen05.ld of the row, mask (`key <= query position`, and not before the
+//                 query's window or its own chunk of positions where the caller names one; with `sink` the denominator has one added;
 //                 crates/models/src/qwen3_5_common/model.rs:154; a warp whose rows see all of a tile's keys skips it, one
 //                 whose rows see none writes zeros), running maximum and sum in 32-bit, probabilities rounded to
 //                 bfloat16 and written over the row's scores in tensor memory
@@ -263,11 +264,17 @@ struct Shared {
 struct Span {
     int last_position, first_tile, n_tiles;
 };
-__device__ __forceinline__ Span span_of(const Item& item, int window) {
+// The oldest key that a query at `position` sees: the window's last position, or the first of the query's own chunk (chunks of
+// `chunk` positions counted from position 0), or 0.  Never decreases with the position.
+__device__ __forceinline__ int first_seen(int position, int window, int chunk) {
+    if (window > 0) return position - window + 1 > 0 ? position - window + 1 : 0;
+    if (chunk > 0) return position / chunk * chunk;
+    return 0;
+}
+__device__ __forceinline__ Span span_of(const Item& item, int window, int chunk) {
     Span span;
     span.last_position = item.position0 + item.rows_here - 1;   // of the last real row
-    int first_key = 0;
-    if (window > 0 && item.position0 - window + 1 > 0) first_key = item.position0 - window + 1;
+    const int first_key = first_seen(item.position0, window, chunk);
     span.first_tile = first_key / BN;
     span.n_tiles = item.rows_here > 0 ? span.last_position / BN - span.first_tile + 1 : 0;
     return span;
@@ -277,8 +284,8 @@ __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap out_map, bf16* __restrict__ out,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start, const int* __restrict__ page_rows,
-                            int page_stride, int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, int n_items,
-                            int* __restrict__ schedule) {
+                            int page_stride, int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, int chunk, int sink,
+                            float out_scale, long long out_stride, int n_items, int* __restrict__ schedule) {
     extern __shared__ uint8_t shared_raw[];
     uint8_t* tiles = shared_raw;                                   // the swizzled tiles need 1,024-byte alignment
     uint8_t* q_tile = tiles;                                       // kHalves slices of [128 rows x 128 bytes]
@@ -396,7 +403,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             bool alive = publish(0, number);
             for (uint32_t k = 0; alive && number >= 0; ++k) {
                 const Item item = shared->item[k & 1];
-                const Span span = span_of(item, window);
+                const Span span = span_of(item, window, chunk);
                 int next = -1;
                 if (span.n_tiles > 0) {
                     const int kv_head = item.head / (n_heads / n_kv_heads);
@@ -487,7 +494,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 const Item item = shared->item[k & 1];
                 barrier_arrive(&shared->item_free[k & 1]);
                 if (item.seq < 0) break;
-                const int n_tiles = span_of(item, window).n_tiles;
+                const int n_tiles = span_of(item, window, chunk).n_tiles;
                 if (n_tiles == 0) continue;
                 alive = barrier_wait(&shared->q_full, n & 1u, abort_flag) && issue_scores(t, n_tiles == 1);
                 for (int i = 0; i < n_tiles && alive; ++i) {
@@ -534,7 +541,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     if (item.seq < 0) break;
                     continue;
                 }
-                const Span span = span_of(item, window);
+                const Span span = span_of(item, window, chunk);
                 n_tiles = span.n_tiles, first_tile = span.first_tile, last_position = span.last_position, position0 = item.position0;
             }
             const int position = position0 + row;
@@ -574,12 +581,13 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 // Which of the tile's keys do this warp's 32 rows see?  All of them (no mask), some (a diagonal tile or a
                 // window's edge: keys [lowest, highest] of the tile are visible to a row), or none.
                 const int warp_first = position0 + warp * 32, warp_last = warp_first + 31;    // positions of the warp's rows
-                const bool all_seen = key0 + BN - 1 <= warp_first && (window == 0 || key0 >= warp_last - window + 1);
-                const bool none_seen = key0 > warp_last || (window > 0 && key0 + BN - 1 < warp_first - window + 1);
+                const bool bounded = window > 0 || chunk > 0;
+                const bool all_seen = key0 + BN - 1 <= warp_first && (!bounded || key0 >= first_seen(warp_last, window, chunk));
+                const bool none_seen = key0 > warp_last || (bounded && key0 + BN - 1 < first_seen(warp_first, window, chunk));
                 if (!all_seen && !none_seen) {
                     const int highest = position - key0;
-                    if (window > 0) {
-                        const int lowest = position - window + 1 - key0;
+                    if (bounded) {
+                        const int lowest = first_seen(position, window, chunk) - key0;
 #pragma unroll
                         for (int j = 0; j < BN; ++j) score[j] = (j <= highest && j >= lowest) ? score[j] : -INFINITY;
                     } else {
@@ -673,7 +681,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             t += n_tiles;
             if (!alive || !barrier_wait(&shared->pv_done, (t - 1) & 1u, abort_flag)) { alive = false; break; }
             tensor_fence_after_sync();
-            const float inverse = 1.0f / sum;
+            // With a sink the denominator has the weight of a key with score 0 and no value added: exp2(0 - used_max) in the sums' scale.
+            // Where that overflows every key's weight is nothing beside it, and the row is zero.
+            const float inverse = out_scale / (sink ? sum + exp2f(-used_max) : sum);
             // Every product of the item is done, so the place of the value tiles is free (the next item's first value tile
             // waits for `staged`): the rows go there as bfloat16 in the layout of the copy engine's swizzled tiles (slices of
             // 64 elements, rows of 128 bytes, the 16-byte pieces of a row exchanged by the row's number, which also keeps
@@ -722,11 +732,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     barrier_arrive(&shared->staged);
                     barrier_arrive(&shared->item_free[k & 1]);
                 }
-                bf16* target = out + (static_cast<size_t>(first_row) * n_heads + head) * D + piece * 8;
+                bf16* target = out + static_cast<size_t>(first_row) * out_stride + head * D + piece * 8;
 #pragma unroll
                 for (int step = 0; step < 32 / kRowsAtOnce; ++step) {
                     const int r = warp * 32 + step * kRowsAtOnce + lane / kPieces;
-                    if (r < rows_here) *reinterpret_cast<uint4*>(target + static_cast<size_t>(r) * n_heads * D) = line[step];
+                    if (r < rows_here) *reinterpret_cast<uint4*>(target + static_cast<size_t>(r) * out_stride) = line[step];
                 }
             }
         }
@@ -762,12 +772,13 @@ EncodeTiled encode_tiled() {
     return function;
 }
 
-// A map over a row-major bfloat16 matrix `[rows, columns]`; boxes of `box_rows` rows by 64 columns (128 bytes), swizzled.
-bool make_map(CUtensorMap* map, const void* base, long long rows, long long columns, int box_rows) {
+// A map over a row-major bfloat16 matrix `[rows, columns]` whose rows lie `row_stride` elements apart (0: `columns`); boxes of
+// `box_rows` rows by 64 columns (128 bytes), swizzled.
+bool make_map(CUtensorMap* map, const void* base, long long rows, long long columns, int box_rows, long long row_stride = 0) {
     EncodeTiled encode = encode_tiled();
     if (!encode) return false;
     const cuuint64_t dims[2] = {static_cast<cuuint64_t>(columns), static_cast<cuuint64_t>(rows)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(columns) * 2};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_stride ? row_stride : columns) * 2};
     const cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_rows)};
     const cuuint32_t element_strides[2] = {1, 1};
     return encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, element_strides,
@@ -790,17 +801,18 @@ TAU_EXPORT int tau_attention_prefill_tc_status() {
 // zero, which the kernel uses and puts back to zero; launches that share them must follow one another on one stream.
 TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, const void* values, void* out, const int* cu_seqlens,
                                         const int* seq_start, const int* page_rows, int page_stride, int page_tokens, long long n_pages,
-                                        int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, int* schedule,
-                                        void* stream) {
+                                        int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, int chunk, int sink,
+                                        float out_scale, long long out_stride, int* schedule, void* stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
     if (!queries || !keys || !values || !out || !cu_seqlens || !seq_start || !page_rows || !schedule || n_heads <= 0 || n_kv_heads <= 0 ||
-        n_heads % n_kv_heads != 0 || page_tokens != BN || window < 0 || n_pages <= 0)
-        return cudaErrorInvalidValue;
+        n_heads % n_kv_heads != 0 || page_tokens != BN || window < 0 || chunk < 0 || (window > 0 && chunk > 0) || n_pages <= 0 ||
+        out_stride < static_cast<long long>(n_heads) * D || out_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0)
+        return cudaErrorInvalidValue;   // the copy engine and the 16-byte stores want output rows that start on 16 bytes
     CUtensorMap q_map, k_map, v_map, out_map;
     const long long cache_rows = n_pages * n_kv_heads * BN;
     if (cache_rows > 0x7fffffffLL) return cudaErrorInvalidValue;   // a tile's row is a 32-bit coordinate of the copy
     if (!make_map(&q_map, queries, n_tokens, static_cast<long long>(n_heads) * D, BM) || !make_map(&k_map, keys, cache_rows, D, BN) ||
-        !make_map(&v_map, values, cache_rows, D, BN) || !make_map(&out_map, out, n_tokens, static_cast<long long>(n_heads) * D, BM))
+        !make_map(&v_map, values, cache_rows, D, BN) || !make_map(&out_map, out, n_tokens, static_cast<long long>(n_heads) * D, BM, out_stride))
         return cudaErrorInvalidValue;
     const int shared_bytes = kQBytes + (kKeyStages + kValueStages) * kKeyBytes + static_cast<int>(sizeof(Shared));
     static int places = 0;   // blocks that the device holds at once
@@ -822,6 +834,6 @@ TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, c
     const int blocks = static_cast<int>(items < places ? items : places);
     tau_launch(attention_prefill_tc_kernel, dim3(blocks), dim3(kThreads), shared_bytes, static_cast<cudaStream_t>(stream), q_map, k_map, v_map,
                out_map, static_cast<bf16*>(out), cu_seqlens, seq_start, page_rows, page_stride, n_seqs, n_tokens, n_heads, n_kv_heads, scale,
-               window, static_cast<int>(items), schedule);
+               window, chunk, sink, out_scale, out_stride, static_cast<int>(items), schedule);
     return tau_launch_status();
 }

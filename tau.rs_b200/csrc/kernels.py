@@ -92,10 +92,14 @@ _CLASS_OF = {
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
 
 
-def start_timing() -> None:
+_timing_by_name = False
+
+
+def start_timing(by_name: bool = False) -> None:
     """From now on an event follows every launch of this library on the current stream; `take_timing` reads them.
-    Meant for steps that run outside a captured graph."""
-    global _timing
+    Meant for steps that run outside a captured graph.  `by_name`: book every launch under its own name instead of its class."""
+    global _timing, _timing_by_name
+    _timing_by_name = by_name
     first = torch.cuda.Event(enable_timing=True)
     first.record()
     _timing = [first, []]
@@ -126,7 +130,7 @@ def _check(status: int, what: str, kernels_launched: int = 1) -> None:
     if _timing is not None and status == 0 and not torch.cuda.is_current_stream_capturing():
         event = torch.cuda.Event(enable_timing=True)
         event.record()
-        _timing[1].append((_CLASS_OF.get(what, "other"), event))
+        _timing[1].append((what if _timing_by_name else _CLASS_OF.get(what, "other"), event))
     if status != 0:
         library = build.load_library("elementwise.cu")
         library.tau_error_string.restype = ctypes.c_char_p
@@ -672,18 +676,22 @@ _prefill_schedule = {}   # (device, stream) -> the two counters by which the blo
 
 
 def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,
-                         scale: float, window: int) -> None:
-    """The same as `attention_prefill` on the tcgen05 tensor cores (accumulators in tensor memory); head sizes 64 and 128."""
+                         scale: float, window: int, chunk: int = 0, sink: bool = False, out_scale: float = 1.0) -> None:
+    """The same as `attention_prefill` on the tcgen05 tensor cores (accumulators in tensor memory); head sizes 64 and 128.
+    Beyond it: with `chunk` a query sees only the keys of its own chunk of `chunk` positions (counted from position 0 of the
+    sequence) instead of a window; with `sink` the softmax's denominator has one added; the result is multiplied by `out_scale`;
+    `out` may be a column range of a wider tensor whose rows start on 16-byte borders."""
     _on_device(queries, keys, values, out, cu_seqlens, seq_start, page_rows)
     tokens = queries.shape[0]
     n_seqs = seq_start.numel()
     _require(head_dim in (64, 128), "the tensor-core prefill kernel serves head sizes 64 and 128")
     _require(queries.dtype == torch.bfloat16 == out.dtype == keys.dtype == values.dtype, "the tensor-core prefill kernel is bfloat16 only")
-    _require(queries.shape == (tokens, n_heads * head_dim) and out.shape == queries.shape and queries.is_contiguous() and out.is_contiguous(),
-             "queries and output must be [tokens, n_heads * head_dim]")
+    _require(queries.shape == (tokens, n_heads * head_dim) and out.shape == queries.shape and queries.is_contiguous() and out.stride(1) == 1
+             and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0, "queries and output must be [tokens, n_heads * head_dim], output rows on 16-byte borders")
     _require(n_heads % n_kv_heads == 0, "n_heads must be a multiple of n_kv_heads")
     _require(keys.shape[1:] == (n_kv_heads, PAGE_TOKENS, head_dim) and keys.is_contiguous() and values.is_contiguous()
              and values.shape == keys.shape, "cache pages must be [pages, n_kv_heads, 64, head_dim]")
+    _require(not (window and chunk), "a window or a chunk, not both")
     _int_vector(cu_seqlens, "cu_seqlens")
     _int_vector(seq_start, "seq_start")
     _require(cu_seqlens.numel() == n_seqs + 1 and page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous()
@@ -696,8 +704,8 @@ def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page
     _check(library.tau_attention_prefill_tc(
         _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(cu_seqlens), _pointer(seq_start), _pointer(page_rows),
         ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_longlong(keys.shape[0]), ctypes.c_int(n_seqs),
-        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window),
-        _pointer(schedule), _stream()),
+        ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk),
+        ctypes.c_int(1 if sink else 0), ctypes.c_float(out_scale), ctypes.c_longlong(out.stride(0)), _pointer(schedule), _stream()),
         "attention_prefill_tc")
 
 
@@ -1221,14 +1229,15 @@ MASKED_MAX_VALUE_DIM = 512
 
 
 def masked_prepare(projected, q_weight, k_weight, eps: float, frequency, rotary_dim: int, magnitude: float, queries, rows, positions, token_seq,
-                   page_rows, n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_rows: bool = True) -> None:
+                   page_rows, n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_rows: bool = True, value_pages=None) -> None:
     """`projected` [tokens, >= n_heads * dim + n_kv_heads * (dim + vdim)] holds queries, keys and values side by side.  With weights
     (float32 [n_heads * dim] and [n_kv_heads * dim]) the queries, and the keys, are divided by the root mean square over their
     whole projection (eps inside the root) and multiplied by the weight.  In every head element `i` of the first `rotary_dim` is
     turned together with element `i + rotary_dim / 2` by `position * frequency[i]`, sine and cosine times `magnitude`.  Queries go
     to `queries` [tokens, n_heads, dim]; with `write_rows` keys and values go to the token's row of the cache pages `rows`
-    [pages, 64, n_kv_heads * (dim + vdim)] as [keys of all heads | values]."""
-    _on_device(projected, q_weight, k_weight, frequency, queries, rows, positions, token_seq, page_rows)
+    [pages, 64, n_kv_heads * (dim + vdim)] as [keys of all heads | values], or, with `value_pages`, to pages of ordinary heads:
+    keys to `rows` [pages, n_kv_heads, 64, dim], values to `value_pages` [pages, n_kv_heads, 64, vdim]."""
+    _on_device(projected, q_weight, k_weight, frequency, queries, rows, positions, token_seq, page_rows, value_pages)
     tokens = projected.shape[0]
     row_width = n_kv_heads * (dim + vdim)
     _require(projected.shape[1] >= n_heads * dim + row_width and projected.stride(1) == 1, "the projection is too narrow")
@@ -1241,35 +1250,42 @@ def masked_prepare(projected, q_weight, k_weight, eps: float, frequency, rotary_
     _int_vector(positions, "positions")
     if write_rows:
         _int_vector(token_seq, "token_seq")
-        _require(rows.shape[1:] == (PAGE_TOKENS, row_width) and rows.is_contiguous() and rows.dtype == projected.dtype, "cache rows must be [pages, 64, row width]")
+        _require_masked_pages(rows, value_pages, projected.dtype, n_kv_heads, dim, vdim)
         _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
     library = build.load_library("masked_attention.cu")
     _check(library.tau_masked_prepare(
         _code(projected), _pointer(projected), ctypes.c_longlong(projected.stride(0)), _pointer(q_weight), _pointer(k_weight), ctypes.c_float(eps),
         _pointer(frequency if rotary_dim else None), ctypes.c_int(rotary_dim), ctypes.c_float(magnitude), _pointer(queries), _pointer(rows if write_rows else None),
-        _pointer(positions), _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1] if write_rows else 0), ctypes.c_int(PAGE_TOKENS),
+        _pointer(value_pages if write_rows else None), _pointer(positions), _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1] if write_rows else 0), ctypes.c_int(PAGE_TOKENS),
         ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_int(1 if write_rows else 0),
         _stream()), "masked_prepare")
 
 
+def _require_masked_pages(rows, value_pages, dtype, n_kv_heads: int, dim: int, vdim: int) -> None:
+    if value_pages is None:
+        _require(rows.shape[1:] == (PAGE_TOKENS, n_kv_heads * (dim + vdim)) and rows.is_contiguous() and rows.dtype == dtype, "cache rows must be [pages, 64, row width]")
+    else:
+        _require(rows.shape[1:] == (n_kv_heads, PAGE_TOKENS, dim) and value_pages.shape == (rows.shape[0], n_kv_heads, PAGE_TOKENS, vdim) and rows.is_contiguous()
+                 and value_pages.is_contiguous() and rows.dtype == value_pages.dtype == dtype, "pages of heads must be [pages, kv heads, 64, dim] and [.., vdim]")
+
+
 def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim: int, scale: float, window: int = 0, chunk: int = 0, sink: bool = False,
-                     out_scale: float = 1.0) -> None:
+                     out_scale: float = 1.0, value_pages=None) -> None:
     """Causal softmax attention of every token over the cached rows of its sequence: within `window` positions (if not 0), or
     within the token's own chunk of `chunk` positions counted from position 0 (if not 0); with `sink` the softmax's denominator has
     one added.  `out` [tokens, n_heads * vdim] (rows any distance apart) receives the result times `out_scale`.  Scores, weights
-    and sums are 32-bit."""
-    _on_device(queries, rows, out, page_rows)
+    and sums are 32-bit.  The cache is `rows`, or `rows` and `value_pages` in the layout of ordinary heads (see `masked_prepare`)."""
+    _on_device(queries, rows, out, page_rows, value_pages)
     tokens, n_heads, dim = queries.shape
-    row_width = n_kv_heads * (dim + vdim)
     _require(queries.is_contiguous() and out.shape == (tokens, n_heads * vdim) and out.stride(1) == 1 and out.dtype == queries.dtype == rows.dtype,
              "queries must be [tokens, n_heads, dim] and the output [tokens, n_heads * vdim]")
-    _require(rows.shape[1:] == (PAGE_TOKENS, row_width) and rows.is_contiguous(), "cache rows must be [pages, 64, row width]")
+    _require_masked_pages(rows, value_pages, queries.dtype, n_kv_heads, dim, vdim)
     _require(vdim <= MASKED_MAX_VALUE_DIM, f"values may have at most {MASKED_MAX_VALUE_DIM} elements per head")
     _require(not (window and chunk), "a window or a chunk, not both")
     _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
     library = build.load_library("masked_attention.cu")
     _check(library.tau_masked_attention(
-        _code(queries), _pointer(queries), _pointer(rows), _pointer(out), ctypes.c_longlong(out.stride(0)), _pointer(step.positions), _pointer(step.token_seq),
+        _code(queries), _pointer(queries), _pointer(rows), _pointer(value_pages), _pointer(out), ctypes.c_longlong(out.stride(0)), _pointer(step.positions), _pointer(step.token_seq),
         _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk), ctypes.c_int(1 if sink else 0),
         ctypes.c_float(out_scale), _stream()), "masked_attention")

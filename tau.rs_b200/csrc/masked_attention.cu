@@ -1,6 +1,7 @@
 // Grouped-query softmax attention over cached rows for heads of any sizes, with the mask and the denominator as parameters:
 //
-//   * key and value sizes may differ (`dim`, `vdim`); one cached row per position holds [kv_heads x key | kv_heads x value];
+//   * key and value sizes may differ (`dim`, `vdim`); one cached row per position holds [kv_heads x key | kv_heads x value], or keys
+//     and values lie in pages of their own in the layout of ordinary heads, [pages, kv_heads, positions of a page, dim or vdim];
 //   * a query at position i sees key j <= i if j > i - window (`window` > 0), or if j lies in i's chunk, floor(j / chunk) ==
 //     floor(i / chunk) (`chunk` > 0; chunks are counted from position 0 of the sequence), or always (both 0);
 //   * `sink`: the denominator of the softmax has exp(0) added (a key with score 0 and no value);
@@ -25,7 +26,7 @@ template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 masked_prepare_kernel(const T* __restrict__ projected, long long projected_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                       float eps, const float* __restrict__ frequency, int rotary, float magnitude, T* __restrict__ queries, T* __restrict__ rows,
-                      const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
+                      T* __restrict__ value_pages, const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
                       int page_tokens, int heads, int kv_heads, int dim, int vdim, int write_rows) {
     grid_dependents_launch();
     grid_dependency_wait();
@@ -59,10 +60,21 @@ masked_prepare_kernel(const T* __restrict__ projected, long long projected_strid
         k_inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(k_width) + eps);
     }
     __syncthreads();      // the turns are complete
+    // Where the token's keys and values go: head `g`'s key at row + g * key_head_stride, its value at value_row + g * value_head_stride.
     T* row = nullptr;
+    T* value_row = nullptr;
+    size_t key_head_stride = dim, value_head_stride = vdim;
     if (write_rows) {
-        const int page = page_rows[static_cast<size_t>(token_seq[token]) * page_stride + position / page_tokens];
-        row = rows + (static_cast<size_t>(page) * page_tokens + position % page_tokens) * (static_cast<size_t>(kv_heads) * (dim + vdim));
+        const size_t page = page_rows[static_cast<size_t>(token_seq[token]) * page_stride + position / page_tokens];
+        const int within_page = position % page_tokens;
+        if (value_pages) {      // keys and values in pages of their own, [pages, kv_heads, page_tokens, dim or vdim]
+            key_head_stride = static_cast<size_t>(page_tokens) * dim, value_head_stride = static_cast<size_t>(page_tokens) * vdim;
+            row = rows + page * kv_heads * key_head_stride + static_cast<size_t>(within_page) * dim;
+            value_row = value_pages + page * kv_heads * value_head_stride + static_cast<size_t>(within_page) * vdim;
+        } else {
+            row = rows + (page * page_tokens + within_page) * (static_cast<size_t>(kv_heads) * (dim + vdim));
+            value_row = row + k_width;
+        }
     }
     // Items: within each head, the `half` rotated pairs, then the dim - rotary elements that pass.
     const int per_head = half + (dim - rotary);
@@ -74,7 +86,7 @@ masked_prepare_kernel(const T* __restrict__ projected, long long projected_strid
         const T* from = source + (is_query ? 0 : q_width) + head * dim;
         const float* weight = is_query ? q_weight : k_weight;
         const float inverse = is_query ? q_inverse : k_inverse;
-        T* target = (is_query ? queries + static_cast<size_t>(token) * q_width : row) + head * dim;
+        T* target = is_query ? queries + static_cast<size_t>(token) * q_width + head * dim : row + head * key_head_stride;
         if (within < half) {
             const int first = within, second = within + half;
             float u = to_float(from[first]) * inverse, w = to_float(from[second]) * inverse;
@@ -94,15 +106,14 @@ masked_prepare_kernel(const T* __restrict__ projected, long long projected_strid
     }
     if (write_rows) {
         const T* values = source + q_width + k_width;
-        T* target = row + k_width;
-        for (int column = threadIdx.x; column < kv_heads * vdim; column += blockDim.x) target[column] = values[column];
+        for (int column = threadIdx.x; column < kv_heads * vdim; column += blockDim.x) value_row[(column / vdim) * value_head_stride + column % vdim] = values[column];
     }
 }
 
 // grid: (tokens, ceil(heads / kWarps)); a warp per head.  Dynamic shared memory: kWarps * dim floats (the queries).
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
-masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ rows, T* __restrict__ out, long long out_stride,
+masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ rows, const T* __restrict__ value_pages, T* __restrict__ out, long long out_stride,
                         const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
                         int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale) {
     grid_dependents_launch();
@@ -118,8 +129,17 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
     const int position = positions[token];
     const int* pages = page_rows + static_cast<size_t>(token_seq[token]) * page_stride;
     const int group = head / (heads / kv_heads);
-    const int row_width = kv_heads * (dim + vdim);
-    const int key_offset = group * dim, value_offset = kv_heads * dim + group * vdim;
+    // Position `r` of page `p`: this head's key at keys + p * key_page + r * key_row, its value at values + p * value_page + r * value_row.
+    const T* keys;
+    const T* values;
+    long long key_page, key_row, value_page, value_row;
+    if (value_pages) {      // [pages, kv_heads, page_tokens, dim or vdim]
+        key_row = dim, value_row = vdim, key_page = static_cast<long long>(kv_heads) * page_tokens * dim, value_page = static_cast<long long>(kv_heads) * page_tokens * vdim;
+        keys = rows + static_cast<long long>(group) * page_tokens * dim, values = value_pages + static_cast<long long>(group) * page_tokens * vdim;
+    } else {                // [pages, page_tokens, keys of all heads | values of all heads]
+        key_row = value_row = kv_heads * (dim + vdim), key_page = value_page = key_row * page_tokens;
+        keys = rows + group * dim, values = rows + kv_heads * dim + group * vdim;
+    }
     int first_key = 0;
     if (window > 0 && position - window + 1 > 0) first_key = position - window + 1;
     if (chunk > 0) first_key = position / chunk * chunk;
@@ -130,11 +150,12 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
     for (int base = first_key; base <= position; base += 32) {
         const int key = base + lane;
         const bool valid = key <= position;
-        long long row_index = 0;
+        long long value_index = 0;
         float score = -INFINITY;
         if (valid) {
-            row_index = static_cast<long long>(pages[key / page_tokens]) * page_tokens + key % page_tokens;
-            const T* k = rows + row_index * row_width + key_offset;
+            const long long page = pages[key / page_tokens], within_page = key % page_tokens;
+            value_index = page * value_page + within_page * value_row;
+            const T* k = keys + page * key_page + within_page * key_row;
             float a = 0.0f, b = 0.0f;
             int column = 0;
             for (; column + 1 < dim; column += 2) {
@@ -154,8 +175,7 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
         const int count = position - base + 1 < 32 ? position - base + 1 : 32;
         for (int j = 0; j < count; ++j) {
             const float w = __shfl_sync(0xffffffffu, p, j);
-            const long long index = __shfl_sync(0xffffffffu, row_index, j);
-            const T* v = rows + index * row_width + value_offset;
+            const T* v = values + __shfl_sync(0xffffffffu, value_index, j);
 #pragma unroll
             for (int i = 0; i < kMaxOwned; ++i) {
                 const int column = lane + 32 * i;
@@ -174,8 +194,8 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
 }  // namespace
 
 TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
-                                  const float* frequency, int rotary, float magnitude, void* queries, void* rows, const int* positions, const int* token_seq,
-                                  const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
+                                  const float* frequency, int rotary, float magnitude, void* queries, void* rows, void* value_pages, const int* positions,
+                                  const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
                                   int write_rows, void* stream) {
     if (tokens <= 0) return 0;
     if (!projected || !queries || !positions || heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || rotary < 0 || rotary > dim || rotary % 2 != 0 ||
@@ -186,7 +206,7 @@ TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long pr
     if (bytes > 40 * 1024) return cudaErrorInvalidValue;
 #define TAU_PREPARE(T)                                                                                                                            \
     tau_launch(masked_prepare_kernel<T>, dim3(tokens), dim3(kWarps * 32), bytes, s, static_cast<const T*>(projected), projected_stride, q_weight, k_weight, eps, \
-               frequency, rotary, magnitude, static_cast<T*>(queries), static_cast<T*>(rows), positions, token_seq, page_rows, page_stride, page_tokens, heads,   \
+               frequency, rotary, magnitude, static_cast<T*>(queries), static_cast<T*>(rows), static_cast<T*>(value_pages), positions, token_seq, page_rows, page_stride, page_tokens, heads,   \
                kv_heads, dim, vdim, write_rows)
     if (dtype == TAU_F32) TAU_PREPARE(float);
     else if (dtype == TAU_BF16) TAU_PREPARE(bf16);
@@ -195,7 +215,9 @@ TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long pr
     return tau_launch_status();
 }
 
-TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* rows, void* out, long long out_stride, const int* positions,
+// `value_pages` null: `rows` holds one row per position, [pages, page_tokens, kv_heads * (dim + vdim)].  Else keys and values lie in pages
+// of their own, `rows` [pages, kv_heads, page_tokens, dim] and `value_pages` [pages, kv_heads, page_tokens, vdim].
+TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
                                     const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
                                     int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, void* stream) {
     if (tokens <= 0) return 0;
@@ -207,7 +229,7 @@ TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* 
     if (bytes > 40 * 1024) return cudaErrorInvalidValue;
     dim3 grid(tokens, (heads + kWarps - 1) / kWarps);
 #define TAU_ATTEND(T)                                                                                                                         \
-    tau_launch(masked_attention_kernel<T>, grid, dim3(kWarps * 32), bytes, s, static_cast<const T*>(queries), static_cast<const T*>(rows), static_cast<T*>(out), \
+    tau_launch(masked_attention_kernel<T>, grid, dim3(kWarps * 32), bytes, s, static_cast<const T*>(queries), static_cast<const T*>(rows), static_cast<const T*>(value_pages), static_cast<T*>(out), \
                out_stride, positions, token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale)
     if (dtype == TAU_F32) TAU_ATTEND(float);
     else if (dtype == TAU_BF16) TAU_ATTEND(bf16);

@@ -66,7 +66,7 @@ def build_pegurax_spec(config: PeguraxConfig) -> ModelSpec:
     for index, block in enumerate(blocks):
         mixer = block.mixer
         if mixer.kind == "side_by_side":
-            group, layer = place(("rows", mixer.left), "rows")
+            group, layer = place(("keys", mixer.left), "keys")
             extra = [("right", *place(("delta", mixer.right.n_heads, mixer.right.key_dim, mixer.right.value_dim), "delta"))]
             if mixer.right.taps > 1:
                 width = 2 * mixer.right.n_key_heads * mixer.right.key_dim + mixer.right.n_heads * mixer.right.value_dim
