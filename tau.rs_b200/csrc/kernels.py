@@ -1221,7 +1221,7 @@ def selective_scan(x, z, pre, bc, a_log, skip, state, cu_seqlens, seq_slot, out)
     library = build.load_library("selective_scan.cu", (f"TAU_SCAN_STATES={states}",))
     _check(library.tau_selective_scan(_code(x), _pointer(x), ctypes.c_longlong(x.stride(0)), _pointer(z), ctypes.c_longlong(z.stride(0)), _pointer(pre),
                                       _pointer(bc), _pointer(a_log), _pointer(skip), _pointer(state), _pointer(cu_seqlens), _pointer(seq_slot), _pointer(out),
-                                      ctypes.c_int(n_seqs), ctypes.c_int(channels), _stream()), "selective_scan")
+                                      ctypes.c_int(n_seqs), ctypes.c_int(tokens), ctypes.c_int(channels), _stream()), "selective_scan")
 
 
 # ---------------------------------------------------------------------------- attention over cached rows with a mask and a sink

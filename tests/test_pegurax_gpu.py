@@ -25,12 +25,12 @@ DEVICE = "cuda"
 
 def close(found, wanted, dtype) -> bool:
     """float32: every logit within 5e-5 of the largest.  bfloat16 (the plain statement rounds nothing): half of the positions within
-    2e-2 of the largest logit and nine in ten within 6e-2; where two experts were a close call the library and the plain statement
-    may choose differently at a position, which says nothing about either (the float32 runs pin every choice)."""
+    2e-2 of the largest logit and all but one in ten (or two) within 6e-2; where two experts were a close call the library and the
+    plain statement may choose differently at a position, which says nothing about either (the float32 runs pin every choice)."""
     if dtype == "float32":
         return relative_error(found, wanted) < TOLERANCE[dtype]
     rows = (found.double() - wanted.double()).abs().amax(dim=-1) / wanted.double().abs().max()
-    return float(rows.median()) < 2e-2 and float(torch.quantile(rows, 0.9)) < 6e-2
+    return float(rows.median()) < 2e-2 and int((rows >= 6e-2).sum()) <= max(2, rows.numel() // 10)
 
 
 def tokens_for(cfg, count, seed):
@@ -79,7 +79,7 @@ def packed_step(runs, slots):
                            all_single=all(count == 1 for count in runs))
 
 
-STEPS = ([1, 9, 2], [1, 1, 1], [1, 1, 1], [2, 1, 6], [1, 1, 1], [5, 2, 1], [40, 3, 1])      # runs of three sequences, step by step
+STEPS = ([1, 9, 2], [1, 1, 1], [1, 1, 1], [2, 1, 6], [1, 1, 1], [5, 2, 1], [40, 3, 1], [150, 1, 67])      # runs of three sequences, step by step
 
 
 # ---- each mechanism's kernels alone -----------------------------------------------------------------------------------
@@ -159,7 +159,7 @@ def test_the_gated_delta_rule_carries_its_state_from_step_to_step(heads, key_hea
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("channels, states", [(50, 1), (30, 5), (80, 8), (64, 16), (70, 32), (33, 64)])
+@pytest.mark.parametrize("channels, states", [(50, 1), (30, 5), (80, 8), (64, 16), (70, 32), (33, 64), (20, 128), (37, 6)])
 def test_the_selective_scan_carries_its_state_from_step_to_step(dtype, channels, states):
     from tau_rs_b200.csrc import kernels
 
