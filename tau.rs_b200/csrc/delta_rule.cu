@@ -8,7 +8,9 @@
 //
 //   prepare:  per token, in 32-bit and in place on [q | k | v] rows: the two unit norms and the query's scale, k . q per key head,
 //             and (g, beta) per value head from the pre-activations.
-//   walk:     one block owns (sequence, head, tile of value columns) and walks the run's tokens in order.  A column of S is shared by
+//   walk:     one block owns (sequence, head, tile of value columns) and walks the run's tokens in order; what the next few tokens
+//             bring (q, k, the tile's values, g, beta, k . q) is on its way into a ring in shared memory meanwhile (cp.async), so that
+//             a token waits for shared memory and one barrier, not for a round trip to memory.  A column of S is shared by
 //             kSplit threads, each with kRows key rows in registers.  With a = S_old^T k and b = S_old^T q (both from the state
 //             before the token, one pass and one barrier) the token's result is u = beta (v - g a), o = g b + u (k . q),
 //             S = g S_old + k u^T: the equations above with the decay pulled out of the sums.
@@ -63,6 +65,15 @@ delta_prepare_kernel(float* __restrict__ rows, long long stride, int q_offset, i
     }
 }
 
+// Four bytes from global to shared memory without passing a register; complete after `copy_wait` and a barrier.
+__device__ __forceinline__ void copy_float(float* target, const float* source) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(target))), "l"(source) : "memory");
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int kRing = 8;      // tokens whose q, k, values and gates are in shared memory or on their way there
+
 template <int kColumns>
 __global__ void __launch_bounds__(kColumns * kSplit)
 delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset, int k_offset, int v_offset, const float* __restrict__ gates,
@@ -70,7 +81,7 @@ delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset
                   const int* __restrict__ seq_slot, float* __restrict__ out, int heads, int key_heads, int value_dim) {
     grid_dependents_launch();
     grid_dependency_wait();
-    __shared__ float qs[2][kDim], ks[2][kDim], part_a[2][kSplit][kColumns], part_b[2][kSplit][kColumns];
+    __shared__ float qs[kRing][kDim], ks[kRing][kDim], vs[kRing][kColumns], scalars[kRing][4], part_a[2][kSplit][kColumns], part_b[2][kSplit][kColumns];
     const int head = blockIdx.x, sequence = blockIdx.y, key_head = head / (heads / key_heads);
     const int local = threadIdx.x % kColumns, part = threadIdx.x / kColumns, row0 = part * kRows;
     const int column = blockIdx.z * kColumns + local;
@@ -81,37 +92,48 @@ delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset
     for (int r = 0; r < kRows; ++r) S[r] = (live && row0 + r < kDim) ? record[row0 + r] : 0.0f;
     const int begin = cu_seqlens[sequence], end = cu_seqlens[sequence + 1];
     constexpr int kStage = (kDim + kColumns * kSplit - 1) / (kColumns * kSplit);
-    auto stage = [&](int token, int half) {      // the token's q and k into one half of shared memory
-        const float* row = rows + static_cast<size_t>(token) * stride;
+    // Asks for token `begin + index` (if the run has it) in its place of the ring; one group of copies per token, empty ones too, so
+    // that the count of groups in flight says which tokens have arrived.
+    auto stage = [&](int index) {
+        const int token = begin + index, place = index % kRing;
+        if (token < end) {
+            const float* row = rows + static_cast<size_t>(token) * stride;
 #pragma unroll
-        for (int i = 0; i < kStage; ++i) {
-            const int d = threadIdx.x + i * kColumns * kSplit;
-            if (d < kDim) {
-                qs[half][d] = row[q_offset + key_head * kDim + d];
-                ks[half][d] = row[k_offset + key_head * kDim + d];
+            for (int i = 0; i < kStage; ++i) {
+                const int d = threadIdx.x + i * kColumns * kSplit;
+                if (d < kDim) {
+                    copy_float(&qs[place][d], row + q_offset + key_head * kDim + d);
+                    copy_float(&ks[place][d], row + k_offset + key_head * kDim + d);
+                }
             }
+            if (part == 0 && live) copy_float(&vs[place][local], row + v_offset + head * value_dim + column);
+            if (threadIdx.x < 2) copy_float(&scalars[place][threadIdx.x], gates + (static_cast<size_t>(token) * heads + head) * 2 + threadIdx.x);
+            if (threadIdx.x == 2) copy_float(&scalars[place][2], kq + static_cast<size_t>(token) * key_heads + key_head);
         }
+        copy_commit();
     };
-    if (begin < end) stage(begin, 0);
+#pragma unroll
+    for (int index = 0; index < kRing - 1; ++index) stage(index);
+    copy_wait<kRing - 2>();      // the first token has arrived
     __syncthreads();
     for (int token = begin; token < end; ++token) {
-        const int half = (token - begin) & 1;
-        // Asked for before the sums, used behind the barrier.
-        const float value = live ? rows[static_cast<size_t>(token) * stride + v_offset + head * value_dim + column] : 0.0f;
-        const float decay = gates[(static_cast<size_t>(token) * heads + head) * 2], beta = gates[(static_cast<size_t>(token) * heads + head) * 2 + 1];
-        const float key_query = kq[static_cast<size_t>(token) * key_heads + key_head];
+        const int index = token - begin, place = index % kRing, half = index & 1;
+        const float value = live ? vs[place][local] : 0.0f;
+        const float decay = scalars[place][0], beta = scalars[place][1], key_query = scalars[place][2];
         float key[kRows];
         float a[2] = {0.0f, 0.0f}, b[2] = {0.0f, 0.0f};
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            key[r] = row0 + r < kDim ? ks[half][row0 + r] : 0.0f;
-            const float query = row0 + r < kDim ? qs[half][row0 + r] : 0.0f;
+            key[r] = row0 + r < kDim ? ks[place][row0 + r] : 0.0f;
+            const float query = row0 + r < kDim ? qs[place][row0 + r] : 0.0f;
             a[r & 1] = fmaf(S[r], key[r], a[r & 1]);
             b[r & 1] = fmaf(S[r], query, b[r & 1]);
         }
         part_a[half][part][local] = a[0] + a[1];
         part_b[half][part][local] = b[0] + b[1];
-        if (token + 1 < end) stage(token + 1, half ^ 1);       // nobody reads that half now: this token's q and k were read above
+        // The place of the token before this one is free: everybody has passed that token's barrier, and read its place before it.
+        stage(index + kRing - 1);
+        copy_wait<kRing - 2>();      // this thread's copies of the next token are done; the barrier shows everybody's
         __syncthreads();
         float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
@@ -124,6 +146,7 @@ delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset
         for (int r = 0; r < kRows; ++r) S[r] = fmaf(decay, S[r], key[r] * update);
         if (part == 0 && live) out[(static_cast<size_t>(token) * heads + head) * value_dim + column] = fmaf(decay, sum_b, update * key_query);
     }
+    copy_wait<0>();
     if (live) {
 #pragma unroll
         for (int r = 0; r < kRows; ++r)
