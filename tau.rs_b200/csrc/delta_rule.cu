@@ -27,6 +27,7 @@ namespace {
 constexpr int kDim = TAU_KEY_DIM;
 constexpr int kSplit = kDim <= 16 ? 1 : kDim <= 32 ? 2 : kDim <= 64 ? 4 : kDim <= 128 ? 8 : kDim <= 256 ? 16 : 32;   // threads that share a column
 constexpr int kRows = (kDim + kSplit - 1) / kSplit;
+constexpr bool kExact = kDim % kSplit == 0;      // every thread's rows exist
 
 // grid: tokens; block: 128.  rows [tokens, stride] float: q at q_offset (key_heads * kDim), k at k_offset.  pre [tokens, 2 heads]:
 // the pre-activations of beta, then of the decay's step.  gates [tokens, heads, 2] = (g, beta); kq [tokens, key_heads].
@@ -72,7 +73,7 @@ __device__ __forceinline__ void copy_float(float* target, const float* source) {
 __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int kRing = 8;      // tokens whose q, k, values and gates are in shared memory or on their way there
+constexpr int kRing = kDim <= 256 ? 8 : 4;      // tokens whose q, k, values and gates are in shared memory or on their way there
 
 template <int kColumns>
 __global__ void __launch_bounds__(kColumns * kSplit)
@@ -81,7 +82,8 @@ delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset
                   const int* __restrict__ seq_slot, float* __restrict__ out, int heads, int key_heads, int value_dim) {
     grid_dependents_launch();
     grid_dependency_wait();
-    __shared__ float qs[kRing][kDim], ks[kRing][kDim], vs[kRing][kColumns], scalars[kRing][4], part_a[2][kSplit][kColumns], part_b[2][kSplit][kColumns];
+    __shared__ __align__(16) float qs[kRing][kDim], ks[kRing][kDim];      // a thread's rows start on 16 bytes where kRows is a multiple of 4
+    __shared__ float vs[kRing][kColumns], scalars[kRing][4], part_a[2][kSplit][kColumns], part_b[2][kSplit][kColumns];
     const int head = blockIdx.x, sequence = blockIdx.y, key_head = head / (heads / key_heads);
     const int local = threadIdx.x % kColumns, part = threadIdx.x / kColumns, row0 = part * kRows;
     const int column = blockIdx.z * kColumns + local;
@@ -124,8 +126,8 @@ delta_rule_kernel(const float* __restrict__ rows, long long stride, int q_offset
         float a[2] = {0.0f, 0.0f}, b[2] = {0.0f, 0.0f};
 #pragma unroll
         for (int r = 0; r < kRows; ++r) {
-            key[r] = row0 + r < kDim ? ks[place][row0 + r] : 0.0f;
-            const float query = row0 + r < kDim ? qs[place][row0 + r] : 0.0f;
+            key[r] = (kExact || row0 + r < kDim) ? ks[place][row0 + r] : 0.0f;
+            const float query = (kExact || row0 + r < kDim) ? qs[place][row0 + r] : 0.0f;
             a[r & 1] = fmaf(S[r], key[r], a[r & 1]);
             b[r & 1] = fmaf(S[r], query, b[r & 1]);
         }

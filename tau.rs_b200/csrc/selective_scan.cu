@@ -148,6 +148,8 @@ selective_scan_tiled_kernel(const T* __restrict__ x, long long x_stride, const T
             const float* buffer = staged + (tile & 1) * kBufferFloats;
             const int token0 = begin + tile * kTile;
             const int count = end - token0 < kTile ? end - token0 : kTile;
+            // Four tokens to a round: only the state's own multiply-add waits for the token before, the rest of the tokens overlap.
+#pragma unroll 4
             for (int i = 0; i < count; ++i) {
                 const int at = i * kTileChannels + local;
                 const float step = buffer[at], drive = buffer[kPlane + at];

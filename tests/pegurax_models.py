@@ -74,6 +74,12 @@ EDGY = config([parallel(softmax_side(heads=4, kv_heads=2, dim=16, vdim=16, chunk
                         left_scale=1.0, right_scale=0.05, mlp=None),
                parallel(softmax_side(heads=2, kv_heads=1, dim=16, vdim=32, chunk=64, rot_dims=16, scale=4.0, scaling=None), delta_side(heads=2, kv_heads=1, dim=8, vdim=8, conv=2),
                         left_scale=1.0, right_scale=0.05, mlp=None)], width=64, vocab=97)
+# The same with keys and values as wide as ordinary heads (64 and 128), which the library keeps in another cache layout and, for runs
+# of tokens in bfloat16, hands to another attention kernel; chunks that no page border divides.
+HEADY = config([parallel(softmax_side(heads=2, kv_heads=1, dim=64, vdim=64, chunk=96, rot_dims=32, scale=2.0), delta_side(heads=2, kv_heads=1, dim=8, vdim=8, conv=4),
+                         left_scale=1.0, right_scale=0.05, mlp=None),
+                parallel(softmax_side(heads=2, kv_heads=2, dim=128, vdim=128, chunk=50, rot_dims=128, scale=1.4, scaling=None), delta_side(heads=2, kv_heads=1, dim=8, vdim=8, conv=2),
+                         left_scale=1.0, right_scale=0.05, mlp=None)], width=64, vocab=97)
 # Recurrences only slowly forgetting, so that a state lost or restarted shows hundreds of tokens later.
 LONG_MEMORY = config([parallel(softmax_side(heads=2, kv_heads=2, dim=8, vdim=8, chunk=16), delta_side(heads=4, kv_heads=1, dim=32, vdim=16, conv=4),
                                left_scale=0.1, right_scale=1.5, mlp=None),

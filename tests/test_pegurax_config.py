@@ -78,6 +78,13 @@ def test_blocks_schedule_and_cache_groups():
                              ((80 * 8,), 1), ((48 * 16,), 1), ((64 * 4,), 1), ((2, 80), 1), ((3, 48), 1), ((1, 64), 1)])
 
 
+def test_keys_and_values_as_wide_as_ordinary_heads_lie_in_pages_of_heads():
+    groups = DecoderModel(spec_from_config_json(pm.HEADY), torch.float32, "cpu").cache_groups()
+    assert not [need for need, _ in groups.values() if need.kind == "rows"]
+    heads = sorted((need.n_kv_heads, need.head_dim, need.chunk, need.window, layers) for need, layers in groups.values() if need.kind == "kv")
+    assert heads == [(1, 64, 96, None, 1), (2, 128, 50, None, 1)]
+
+
 def test_one_tap_keeps_no_tail():
     spec = spec_from_config_json(pm.ODD)
     assert [role for role, _, _ in spec.schedule[0].extra_cache] == ["right"] and spec.schedule[1].extra_cache == ()

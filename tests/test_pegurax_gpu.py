@@ -51,7 +51,7 @@ def plain_logits(cfg, values, tokens):
 def models(tmp_path_factory):
     root = tmp_path_factory.mktemp("pegurax")
     made = {}
-    for name, cfg, seed, slow in (("mixed", pm.MIXED, 11, False), ("odd", pm.ODD, 12, False), ("peaky", pm.PEAKY, 14, False), ("edgy", pm.EDGY, 15, False),
+    for name, cfg, seed, slow in (("mixed", pm.MIXED, 11, False), ("odd", pm.ODD, 12, False), ("peaky", pm.PEAKY, 14, False), ("edgy", pm.EDGY, 15, False), ("heady", pm.HEADY, 17, False),
                                   ("long_memory", pm.LONG_MEMORY, 16, True)):
         folder = str(root / name)
         made[name] = (folder, cfg, pm.write_model(folder, cfg, seed, slow_decay=slow))
@@ -406,7 +406,7 @@ def test_the_residual_stream_after_every_layer(models):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "long_memory"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "long_memory", "heady"])
 def test_portions_down_to_two_tokens_and_page_borders(models, name, dtype):
     engine, cfg, values = engine_of(models, name, dtype)
     tokens = tokens_for(cfg, 330, 22)
@@ -423,7 +423,7 @@ def test_portions_down_to_two_tokens_and_page_borders(models, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["peaky", "edgy"])
+@pytest.mark.parametrize("name", ["peaky", "edgy", "heady"])
 def test_a_sharp_softmax_loses_no_key_far_back_at_a_page_border_or_at_a_chunk_edge(models, name, dtype):
     engine, cfg, values = engine_of(models, name, dtype)
     tokens = tokens_for(cfg, 400, 23)
@@ -438,7 +438,7 @@ def test_a_sharp_softmax_loses_no_key_far_back_at_a_page_border_or_at_a_chunk_ed
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["mixed", "odd", "edgy"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "edgy", "heady"])
 def test_unequal_batches_against_each_request_alone(models, name, dtype):
     engine, cfg, values = engine_of(models, name, dtype, 2048)
     lengths, prompts = [90, 31, 140, 5, 66], [70, 1, 129, 3, 64]
