@@ -315,12 +315,13 @@ def bisudra_sizes():
 
 def pegurax_sizes():
     """Layer sizes that resemble a real model of Pegurax's kind: layers whose mixer is a chunked softmax attention (128-element heads, 8
-    key/value heads, chunks of 1,024 positions) beside a gated delta rule (128 by 128 states, half as many key heads as heads, 4 taps)
+    key/value heads, chunks of 1,536 positions, so that a prompt of 2,048 crosses a chunk's edge and a token decoded behind it still reads 512
+    keys) beside a gated delta rule (128 by 128 states, half as many key heads as heads, 4 taps)
     alternate with selective scans (twice the width inside, 16 states per channel, 4 taps); the feed-forwards are dense, four times the
     width, or 32 experts of which 4 are chosen.  Beside it the closest design that was here before, Fasesun (attention, matrix-state
     recurrences and routed experts as well), and a dense Qwen3, each of the same width, depth and vocabulary."""
     def pegurax(width, heads, expert_ff):
-        left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1024},
+        left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 1536},
                 "rot": {"base": 10000.0, "dims": 128, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
         right = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4}
         parallel = {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}
