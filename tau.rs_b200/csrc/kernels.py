@@ -1270,11 +1270,13 @@ def _require_masked_pages(rows, value_pages, dtype, n_kv_heads: int, dim: int, v
 
 
 def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim: int, scale: float, window: int = 0, chunk: int = 0, sink: bool = False,
-                     out_scale: float = 1.0, value_pages=None) -> None:
+                     out_scale: float = 1.0, value_pages=None, staged: bool = False) -> None:
     """Causal softmax attention of every token over the cached rows of its sequence: within `window` positions (if not 0), or
     within the token's own chunk of `chunk` positions counted from position 0 (if not 0); with `sink` the softmax's denominator has
     one added.  `out` [tokens, n_heads * vdim] (rows any distance apart) receives the result times `out_scale`.  Scores, weights
-    and sums are 32-bit.  The cache is `rows`, or `rows` and `value_pages` in the layout of ordinary heads (see `masked_prepare`)."""
+    and sums are 32-bit.  The cache is `rows`, or `rows` and `value_pages` in the layout of ordinary heads (see `masked_prepare`).
+    `staged` (meant for steps of single tokens) asks for the kernel that stages tiles of the cache in shared memory and shares them
+    among the heads of a key/value head; sizes that it does not serve take the other kernel."""
     _on_device(queries, rows, out, page_rows, value_pages)
     tokens, n_heads, dim = queries.shape
     _require(queries.is_contiguous() and out.shape == (tokens, n_heads * vdim) and out.stride(1) == 1 and out.dtype == queries.dtype == rows.dtype,
@@ -1288,7 +1290,7 @@ def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim:
         _code(queries), _pointer(queries), _pointer(rows), _pointer(value_pages), _pointer(out), ctypes.c_longlong(out.stride(0)), _pointer(step.positions), _pointer(step.token_seq),
         _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk), ctypes.c_int(1 if sink else 0),
-        ctypes.c_float(out_scale), _stream()), "masked_attention")
+        ctypes.c_float(out_scale), ctypes.c_int(1 if staged else 0), _stream()), "masked_attention")
 
 
 # ---------------------------------------------------------------------------- routed experts

@@ -191,6 +191,182 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
     }
 }
 
+// ---- single tokens (and any step whose sizes allow): tiles of keys and values staged in shared memory --------------------------
+//
+// grid: (tokens, kv_heads * ceil(group / kStagedWarps)); block: kStagedWarps warps, one per query head of the key/value head's group.
+// All threads bring tiles of 32 positions into shared memory with cp.async, 4 bytes at a time (rows of the cache lie 4-byte
+// aligned because dim and vdim are multiples of a word's elements), two tiles deep, so that the group's heads share one pass over
+// the cache and the loads are whole rows.  Key rows are an odd number of words apart: lane j reads key j without bank conflicts.
+// Then as above: a lane scores one key, every lane sums its own value columns; maximum, weights and sums in 32-bit.
+constexpr int kStagedWarps = 4;
+constexpr int kTileKeys = 32;
+
+__device__ __forceinline__ void copy_word(void* target, const void* source) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(target))), "l"(source) : "memory");
+}
+__device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+template <typename T> struct Word;
+template <> struct Word<float> {
+    static constexpr int kElements = 1;
+    static __device__ __forceinline__ float first(uint32_t word) { return __uint_as_float(word); }
+    static __device__ __forceinline__ float second(uint32_t) { return 0.0f; }
+};
+template <> struct Word<bf16> {
+    static constexpr int kElements = 2;
+    static __device__ __forceinline__ float first(uint32_t word) { return __uint_as_float(word << 16); }
+    static __device__ __forceinline__ float second(uint32_t word) { return __uint_as_float(word & 0xffff0000u); }
+};
+
+__host__ __device__ inline int key_stride_words(int key_words) { return key_words | 1; }
+
+template <typename T>
+__global__ void __launch_bounds__(kStagedWarps * 32)
+masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restrict__ rows, const T* __restrict__ value_pages, T* __restrict__ out,
+                               long long out_stride, const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows,
+                               int page_stride, int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink,
+                               float out_scale) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    constexpr int kPer = Word<T>::kElements;
+    extern __shared__ __align__(16) uint32_t staged_words[];
+    const int key_words = dim / kPer, value_words = vdim / kPer, key_stride = key_stride_words(key_words);
+    const int tile_words = kTileKeys * (key_stride + value_words);
+    float* query_rows = reinterpret_cast<float*>(staged_words + 2 * tile_words);       // [kStagedWarps][dim]
+    const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int group_size = heads / kv_heads, passes = (group_size + kStagedWarps - 1) / kStagedWarps;
+    const int group = blockIdx.y / passes, head_in_group = (blockIdx.y % passes) * kStagedWarps + warp;
+    const bool has_head = head_in_group < group_size;
+    const int head = group * group_size + (has_head ? head_in_group : 0);
+    const int position = positions[token];
+    const int* pages = page_rows + static_cast<size_t>(token_seq[token]) * page_stride;
+    const T* keys;
+    const T* values;
+    long long key_page, key_row, value_page, value_row;
+    if (value_pages) {
+        key_row = dim, value_row = vdim, key_page = static_cast<long long>(kv_heads) * page_tokens * dim, value_page = static_cast<long long>(kv_heads) * page_tokens * vdim;
+        keys = rows + static_cast<long long>(group) * page_tokens * dim, values = value_pages + static_cast<long long>(group) * page_tokens * vdim;
+    } else {
+        key_row = value_row = kv_heads * (dim + vdim), key_page = value_page = key_row * page_tokens;
+        keys = rows + group * dim, values = rows + kv_heads * dim + group * vdim;
+    }
+    int first_key = 0;
+    if (window > 0 && position - window + 1 > 0) first_key = position - window + 1;
+    if (chunk > 0) first_key = position / chunk * chunk;
+    const int n_tiles = (position - first_key) / kTileKeys + 1;
+
+    auto stage = [&](int tile) {
+        uint32_t* buffer = staged_words + (tile & 1) * tile_words;
+        if (tile < n_tiles) {
+            const int base = first_key + tile * kTileKeys;
+            const int count = position - base + 1 < kTileKeys ? position - base + 1 : kTileKeys;
+            for (int i = threadIdx.x; i < count * key_words; i += kStagedWarps * 32) {
+                const int row = i / key_words, word = i - row * key_words, key = base + row;
+                const T* source = keys + pages[key / page_tokens] * key_page + (key % page_tokens) * key_row;
+                copy_word(buffer + row * key_stride + word, reinterpret_cast<const uint32_t*>(source) + word);
+            }
+            uint32_t* value_buffer = buffer + kTileKeys * key_stride;
+            for (int i = threadIdx.x; i < count * value_words; i += kStagedWarps * 32) {
+                const int row = i / value_words, word = i - row * value_words, key = base + row;
+                const T* source = values + pages[key / page_tokens] * value_page + (key % page_tokens) * value_row;
+                copy_word(value_buffer + row * value_words + word, reinterpret_cast<const uint32_t*>(source) + word);
+            }
+        }
+        copy_commit();
+    };
+    stage(0);
+    stage(1);
+    if (has_head)
+        for (int column = lane; column < dim; column += 32)
+            query_rows[warp * dim + column] = to_float(queries[(static_cast<size_t>(token) * heads + head) * dim + column]) * scale;
+    const float* query = query_rows + warp * dim;
+    float top = sink ? 0.0f : -INFINITY, sum = sink ? 1.0f : 0.0f;
+    float acc[kMaxOwned];
+#pragma unroll
+    for (int i = 0; i < kMaxOwned; ++i) acc[i] = 0.0f;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        copy_wait<1>();      // this thread's copies of `tile` are done (those of the next tile may be on their way)
+        __syncthreads();     // everybody's are; the queries too
+        const uint32_t* buffer = staged_words + (tile & 1) * tile_words;
+        const int base = first_key + tile * kTileKeys;
+        const int count = position - base + 1 < kTileKeys ? position - base + 1 : kTileKeys;
+        if (has_head) {
+            float score = -INFINITY;
+            if (lane < count) {
+                const uint32_t* k = buffer + lane * key_stride;
+                float a = 0.0f, b = 0.0f;
+                for (int word = 0; word < key_words; ++word) {
+                    const uint32_t both = k[word];
+                    a = fmaf(query[word * kPer], Word<T>::first(both), a);
+                    if (kPer == 2) b = fmaf(query[word * kPer + 1], Word<T>::second(both), b);
+                }
+                score = a + b;
+            }
+            const float new_top = fmaxf(top, warp_max(score));
+            const float p = lane < count ? expf(score - new_top) : 0.0f;
+            const float keep = expf(top - new_top);
+            sum = sum * keep + warp_sum(p);
+            top = new_top;
+#pragma unroll
+            for (int i = 0; i < kMaxOwned; ++i) acc[i] *= keep;
+            const uint32_t* v = buffer + kTileKeys * key_stride;
+            for (int j = 0; j < count; ++j) {
+                const float w = __shfl_sync(0xffffffffu, p, j);
+#pragma unroll
+                for (int i = 0; i < kMaxOwned / kPer; ++i) {
+                    const int word = lane + 32 * i;
+                    if (word < value_words) {
+                        const uint32_t both = v[j * value_words + word];
+                        acc[i * kPer] = fmaf(w, Word<T>::first(both), acc[i * kPer]);
+                        if (kPer == 2) acc[i * kPer + 1] = fmaf(w, Word<T>::second(both), acc[i * kPer + 1]);
+                    }
+                }
+            }
+        }
+        __syncthreads();     // the tile's place may be written over
+        stage(tile + 2);
+    }
+    copy_wait<0>();
+    if (!has_head) return;
+    const float factor = out_scale / sum;
+    T* target = out + static_cast<size_t>(token) * out_stride + head * vdim;
+#pragma unroll
+    for (int i = 0; i < kMaxOwned / kPer; ++i) {
+        const int word = lane + 32 * i;
+        if (word < value_words) {
+            target[word * kPer] = from_float<T>(acc[i * kPer] * factor);
+            if (kPer == 2) target[word * kPer + 1] = from_float<T>(acc[i * kPer + 1] * factor);
+        }
+    }
+}
+
+// Shared memory of the staged kernel, or 0 where it does not serve these sizes.
+template <typename T>
+int staged_bytes(int dim, int vdim) {
+    constexpr int kPer = Word<T>::kElements;
+    if (dim % kPer != 0 || vdim % kPer != 0) return 0;
+    const long long bytes = (2LL * kTileKeys * (key_stride_words(dim / kPer) + vdim / kPer) + static_cast<long long>(kStagedWarps) * dim) * 4;
+    return bytes <= 160 * 1024 ? static_cast<int>(bytes) : 0;
+}
+
+template <typename T>
+int launch_staged(int bytes, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
+                  const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
+                  float scale, int window, int chunk, int sink, float out_scale, cudaStream_t s) {
+    static int allowed = 48 * 1024;
+    if (bytes > allowed) {
+        cudaError_t status = cudaFuncSetAttribute(masked_attention_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+        if (status != cudaSuccess) return static_cast<int>(status);
+        allowed = 160 * 1024;
+    }
+    const int group_size = heads / kv_heads, passes = (group_size + kStagedWarps - 1) / kStagedWarps;
+    tau_launch(masked_attention_staged_kernel<T>, dim3(tokens, kv_heads * passes), dim3(kStagedWarps * 32), bytes, s, static_cast<const T*>(queries),
+               static_cast<const T*>(rows), static_cast<const T*>(value_pages), static_cast<T*>(out), out_stride, positions, token_seq, page_rows, page_stride,
+               page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale);
+    return tau_launch_status();
+}
+
 }  // namespace
 
 TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
@@ -219,12 +395,23 @@ TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long pr
 // of their own, `rows` [pages, kv_heads, page_tokens, dim] and `value_pages` [pages, kv_heads, page_tokens, vdim].
 TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
                                     const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
-                                    int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, void* stream) {
+                                    int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, int staged, void* stream) {
     if (tokens <= 0) return 0;
     if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim <= 0 ||
         vdim <= 0 || vdim > 32 * kMaxOwned || window < 0 || chunk < 0 || (window > 0 && chunk > 0))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // `staged` (steps of single tokens): the kernel that shares tiles of the cache among a group's heads, where the sizes allow it.
+    if (staged && (dtype == TAU_F32 || dtype == TAU_BF16)) {
+        const int staged_size = dtype == TAU_F32 ? staged_bytes<float>(dim, vdim) : staged_bytes<bf16>(dim, vdim);
+        if (staged_size > 0) {
+            if (dtype == TAU_F32)
+                return launch_staged<float>(staged_size, queries, rows, value_pages, out, out_stride, positions, token_seq, page_rows, page_stride, page_tokens,
+                                            tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, s);
+            return launch_staged<bf16>(staged_size, queries, rows, value_pages, out, out_stride, positions, token_seq, page_rows, page_stride, page_tokens,
+                                       tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, s);
+        }
+    }
     const size_t bytes = static_cast<size_t>(kWarps) * dim * sizeof(float);
     if (bytes > 40 * 1024) return cudaErrorInvalidValue;
     dim3 grid(tokens, (heads + kWarps - 1) / kWarps);

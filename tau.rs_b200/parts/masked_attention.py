@@ -93,4 +93,4 @@ class MaskedAttention(JoinableMixer):
                                          spec.dim, spec.softmax_scale, spec.window or 0, spec.chunk or 0, spec.sink, self.out_scale)
             return
         kernels.masked_attention(queries, keys, out, step, pages, spec.n_kv_heads, spec.value_dim, spec.softmax_scale, spec.window or 0,
-                                 spec.chunk or 0, spec.sink, self.out_scale, values)
+                                 spec.chunk or 0, spec.sink, self.out_scale, values, staged=step.all_single)

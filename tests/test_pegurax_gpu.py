@@ -199,7 +199,7 @@ def attention_pages(mixer, pages, dtype, fill):
     return torch.full((pages, 64, kv_heads * (dim + vdim)), fill, dtype=TORCH[dtype], device=DEVICE)
 
 
-def run_masked_attention(h, W, mixer, eps, dtype, positions, page_of, cache, out_scale=1.0):
+def run_masked_attention(h, W, mixer, eps, dtype, positions, page_of, cache, out_scale=1.0, staged=None):
     """`h` [tokens, width] of one sequence through the stacked projection in 64-bit, then the library's kernels over a paged cache
     whose pages are `page_of[position // 64]`, in the layout of `cache` (see `attention_pages`): the mixer's own two kernels, or, for
     a run of new tokens in bfloat16 over pages of ordinary heads, the tensor-core kernel behind the first of them."""
@@ -218,12 +218,13 @@ def run_masked_attention(h, W, mixer, eps, dtype, positions, page_of, cache, out
     out = torch.zeros((tokens, heads * vdim + 8), dtype=TORCH[dtype], device=DEVICE)
     kernels.masked_prepare(projected, on_device(W["m.q.norm"]), on_device(W["m.k.norm"]), eps, frequency, rotary, magnitude, queries, keys, step.positions,
                            step.token_seq, pages, heads, kv_heads, dim, vdim, True, values)
-    if values is not None and dtype == "bfloat16" and tokens > 1:
+    if values is not None and dtype == "bfloat16" and tokens > 1 and not staged:
         kernels.attention_prefill_tc(queries.view(tokens, -1), keys, values, out[:, : heads * vdim], step.cu_seqlens, step.seq_start, pages, heads, kv_heads, dim,
                                      mixer["scale"], 0, mixer["mask"]["size"], True, out_scale)
         assert kernels.attention_prefill_tc_status(dim) == 0
     else:
-        kernels.masked_attention(queries, keys, out[:, : heads * vdim], step, pages, kv_heads, vdim, mixer["scale"], 0, mixer["mask"]["size"], True, out_scale, values)
+        kernels.masked_attention(queries, keys, out[:, : heads * vdim], step, pages, kv_heads, vdim, mixer["scale"], 0, mixer["mask"]["size"], True, out_scale, values,
+                                 staged=tokens == 1 if staged is None else staged)      # single tokens take the staged kernel, as in the library
     assert float(out[:, heads * vdim :].float().abs().max()) == 0.0
     return out[:, : heads * vdim].float().cpu()
 
@@ -260,6 +261,9 @@ def test_chunked_attention_kernels_over_scattered_pages(dtype, heads, kv_heads, 
         assert torch.isnan(pool[[2, 3, 5, 7]].float()).all()          # nothing was written outside the sequence's pages
     scaled = run_masked_attention(h[:150], W, mixer, eps, dtype, list(range(150)), page_of, rows, out_scale=-0.6)
     assert relative_error(scaled, -0.6 * wanted[:150]) < (2e-5 if dtype == "float32" else 3e-2)
+    # the kernel of single tokens on every position of the sequence at once: tiles of 32 keys, whole and ragged, from a chunk's first key on
+    tiled = run_masked_attention(h, W, mixer, eps, dtype, list(range(total)), page_of, rows, out_scale=0.5, staged=True)
+    assert relative_error(tiled, 0.5 * wanted) < (2e-5 if dtype == "float32" else 3e-2)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
