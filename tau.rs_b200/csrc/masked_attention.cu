@@ -261,16 +261,14 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
         if (tile < n_tiles) {
             const int base = first_key + tile * kTileKeys;
             const int count = position - base + 1 < kTileKeys ? position - base + 1 : kTileKeys;
-            for (int i = threadIdx.x; i < count * key_words; i += kStagedWarps * 32) {
-                const int row = i / key_words, word = i - row * key_words, key = base + row;
-                const T* source = keys + pages[key / page_tokens] * key_page + (key % page_tokens) * key_row;
-                copy_word(buffer + row * key_stride + word, reinterpret_cast<const uint32_t*>(source) + word);
-            }
             uint32_t* value_buffer = buffer + kTileKeys * key_stride;
-            for (int i = threadIdx.x; i < count * value_words; i += kStagedWarps * 32) {
-                const int row = i / value_words, word = i - row * value_words, key = base + row;
-                const T* source = values + pages[key / page_tokens] * value_page + (key % page_tokens) * value_row;
-                copy_word(value_buffer + row * value_words + word, reinterpret_cast<const uint32_t*>(source) + word);
+            for (int row = warp; row < count; row += kStagedWarps) {      // a warp per row: one page lookup, then whole lines
+                const int key = base + row;
+                const long long page = pages[key / page_tokens], within_page = key % page_tokens;
+                const uint32_t* key_source = reinterpret_cast<const uint32_t*>(keys + page * key_page + within_page * key_row);
+                const uint32_t* value_source = reinterpret_cast<const uint32_t*>(values + page * value_page + within_page * value_row);
+                for (int word = lane; word < key_words; word += 32) copy_word(buffer + row * key_stride + word, key_source + word);
+                for (int word = lane; word < value_words; word += 32) copy_word(value_buffer + row * value_words + word, value_source + word);
             }
         }
         copy_commit();
