@@ -101,7 +101,7 @@ def test_the_model_asks_for_exactly_the_tensors_of_the_design():
 
 def test_the_rotations_frequencies():
     for rot in (pm.softmax_side()["rot"], pm.softmax_side(rot_dims=16, scaling=pm.yarn(8.0, 512, 32.0, 1.0))["rot"], pm.softmax_side(scaling=None)["rot"],
-                pm.softmax_side(dim=64, rot_dims=64, base=250000.0, scaling=pm.yarn(2.0, 20, 3.0, 1.5))["rot"]):
+                pm.softmax_side(dim=64, rot_dims=64, base=40000.0, scaling=pm.yarn(2.0, 20, 3.0, 1.5))["rot"]):
         scaling = rot.get("scaling") or {}
         part = build("position", ScaledRotationSpec(rotary_dim=rot["dims"], theta=rot["base"], factor=scaling.get("factor"), original=scaling.get("original", 0.0),
                                                     fast=scaling.get("fast", 0.0), slow=scaling.get("slow", 0.0)), device="cpu")
