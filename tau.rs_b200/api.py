@@ -57,6 +57,12 @@ def load_model(folder: str, dtype: str = "auto", device="gpu", enforce_declared_
     run_dtype = resolve_dtype(dtype, metadata.declared_dtype)
     if enforce_declared_dtype:
         run_dtype = validate_run_dtype(metadata, run_dtype)
+    if entry.complete_config is not None:      # sizes that only the tensors' shapes give
+        from .weights.safetensors_io import SafetensorsFolder
+
+        found = SafetensorsFolder(folder)
+        raw = entry.complete_config(raw, {name: tuple(info.shape) for name, info in found.tensors.items()})
+        found.close()
     spec = entry.build_spec(entry.parse_config(raw))
     target = device if isinstance(device, torch.device) else resolve_device(device)
     model = DecoderModel(spec, _TORCH_DTYPE[run_dtype], target)

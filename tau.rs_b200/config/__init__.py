@@ -7,6 +7,7 @@ from .registry import (Architecture, architecture_for, register_architecture, re
 from .fasesun import FasesunConfig
 from .bisudra import BisudraConfig
 from .pegurax import PeguraxConfig
-from .specs import (AttentionSpec, BlockSpec, DeltaRuleSpec, DenseFeedForwardSpec, DifferentialAttentionSpec, MaskedAttentionSpec, SandwichBlockSpec,
+from .nugolorn import NugolornConfig
+from .specs import (AttentionSpec, BlockSpec, ChannelDecayMemorySpec, DeltaRuleSpec, DenseFeedForwardSpec, DifferentialAttentionSpec, MaskedAttentionSpec, SandwichBlockSpec,
                     ScaledRotationSpec, SelectiveScanSpec, SideBySideSpec, LatentAttentionSpec, LinearRecurrenceSpec, ModelSpec, NormSpec, PairRotationSpec,
                     PositionSpec, RoutedExpertsSpec, ScheduleEntry, SublayerNormBlockSpec, SwiGLUSpec, TokenSideSpec)

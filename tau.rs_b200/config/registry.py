@@ -24,13 +24,15 @@ class Architecture:
     build_spec: Callable[[object], ModelSpec]
     # The dtype that a folder of this architecture holds when its config.json declares none (None: float32 alone runs then).
     storage_dtype: Optional[str] = None
+    # Writes sizes that only the shapes of a folder's tensors give into the raw configuration: (config.json, name -> shape) -> config.json.
+    complete_config: Optional[Callable[[dict, dict], dict]] = None
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, model_type: str, parse_config, build_spec, storage_dtype: Optional[str] = None) -> Architecture:
-    entry = Architecture(name, model_type, parse_config, build_spec, storage_dtype)
+def register_architecture(name: str, model_type: str, parse_config, build_spec, storage_dtype: Optional[str] = None, complete_config=None) -> Architecture:
+    entry = Architecture(name, model_type, parse_config, build_spec, storage_dtype, complete_config)
     _ARCHITECTURES[name] = entry
     return entry
 

@@ -16,13 +16,15 @@ from typing import Optional, Tuple
 @dataclass(frozen=True)
 class NormSpec:
     """`kind == "rms_norm"`: `x / sqrt(mean(x^2) + eps) * w`.  `kind == "layer_norm"`: `(x - mean) / sqrt(variance + eps) * w + b`,
-    the bias being the tensor `<weight's name><bias_suffix>`."""
+    the bias being the tensor `<weight's name><bias_suffix>`.  With `groups` > 1 an RMS norm cuts the row into that many equal
+    consecutive pieces and divides each by its own root mean square (on a residual stream kept in 32-bit)."""
 
     width: int
     eps: float
     kind: str = "rms_norm"
     bias_suffix: str = ".bias"
     bias: bool = True          # a layer norm without a bias has no such tensor
+    groups: int = 1
 
 
 @dataclass(frozen=True)
@@ -195,7 +197,16 @@ class MaskedAttentionSpec:
     position (or over pages of ordinary heads where the sizes allow the tensor-core kernel).  `qk_norm == "projection"`: queries, and keys, pass an RMS norm over their whole projection (all heads at once) with a
     weight of that size, before `position`.  A query at position i sees key j <= i within `window` positions, or (with `chunk`)
     only if floor(j / chunk) == floor(i / chunk), chunks counted from position 0.  `sink`: one is added to the softmax's
-    denominator (a key with score 0 and no value).  `out_scale` multiplies what the output projection reads."""
+    denominator (a key with score 0 and no value).  `out_scale` multiplies what the output projection reads.
+
+    `bias`: q, k and v have biases (`<name>.b`).  `taps` > 0: q, k and v each pass a causal convolution of that many taps over time
+    per channel directly behind the projection (`<name>.conv` [channels, taps], no bias, no activation), whose last `taps - 1`
+    inputs are state of the sequence.  `temperature` = (coef, every): the query at position p is multiplied by
+    `1 + coef * ln(floor((p + 1) / every) + 1)`.  `distance_bias`: `r1 * ln(1 + r2 * (i - j))` is taken off the score, with one r1 and
+    one r2 per head (`r1`, `r2`).  `weights == "sigmoid"`: no softmax; a visible key weighs `sigmoid(score + pb[head])` (`pb`, one
+    number per head), not normalised over the keys.  `gate`: `"head"` multiplies each head's result by the sigmoid of one number per
+    head, `"element"` every element by the sigmoid of its own (`g`, a projection of the mixer's input).  `own_keys=False`: the
+    layer has no key and value tensors and reads the keys and values that another layer of the same sizes cached."""
 
     hidden: int
     n_heads: int
@@ -210,6 +221,13 @@ class MaskedAttentionSpec:
     chunk: Optional[int] = None
     sink: bool = False
     kind: str = "masked_attention"
+    bias: bool = False
+    taps: int = 0
+    temperature: Optional[Tuple[float, int]] = None
+    distance_bias: bool = False
+    weights: str = "softmax"
+    gate: Optional[str] = None
+    own_keys: bool = True
 
 
 @dataclass(frozen=True)
@@ -218,7 +236,12 @@ class DeltaRuleSpec:
     u^T; o = S^T q`.  Queries and keys belong to `n_key_heads` heads (value head h reads key head h / (n_heads / n_key_heads)).
     q, k and v each pass a causal convolution of `taps` taps per channel and SiLU; q and k are then unit vectors per head, q times
     `key_dim^-1/2`; `beta = sigmoid(W_b h)`; `g = exp(-exp(A_log) softplus(W_a h + dt_bias))`.  Each head's read-out is divided by
-    its root mean square (`eps`), times a weight of `value_dim` elements shared by the heads, times `silu(W_g h)`."""
+    its root mean square (`eps`), times a weight of `value_dim` elements shared by the heads, times `silu(W_g h)`.
+
+    `decay == "channel"`: g is a vector over the state's rows, one decay per head and key channel, from pre-activations laid out
+    heads x key_dim (`dt_bias` is then as wide; `A_log` stays one number per head).  `decay_rank` > 0: the decay's pre-activation is
+    `W_a2 (W_a1 h)` through that many numbers (`a1`, `a2`) instead of `W_a h`; `gate_rank` > 0 likewise `W_g2 (W_g1 h)` (`g1`, `g2`)
+    for the output gate.  `gate_activation`: `"silu"` or `"sigmoid"`."""
 
     hidden: int
     n_heads: int
@@ -228,6 +251,26 @@ class DeltaRuleSpec:
     taps: int
     eps: float
     kind: str = "gated_delta_rule"
+    decay: str = "head"
+    decay_rank: int = 0
+    gate_rank: int = 0
+    gate_activation: str = "silu"
+
+
+@dataclass(frozen=True)
+class ChannelDecayMemorySpec:
+    """Time mixing with a matrix state per head (`key_dim` x `key_dim`), a decay per key channel and a bonus for the token itself:
+    with h' the input of the token before (zeros for the first token) every projection reads its own mix `h + (h' - h) * mu_s`;
+    `r`, `k`, `v` are projections of their mixes, `gate = silu(W_g mix_g)`, `w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0))` through
+    `decay_rank` numbers; per head `o = (S + diag(u) k v^T)^T r`, then `S <- diag(w) S + k v^T`; each head's `o` is divided by its
+    root mean square (`eps`), times `norm`, times the gate, then `W_o`."""
+
+    hidden: int
+    n_heads: int
+    key_dim: int
+    decay_rank: int
+    eps: float
+    kind: str = "channel_decay_memory"
 
 
 @dataclass(frozen=True)
@@ -247,7 +290,8 @@ class SelectiveScanSpec:
 @dataclass(frozen=True)
 class SideBySideSpec:
     """Two mixers that read the same input; the result is `left_scale * left(h) + right_scale * right(h)`.  Their tensors lie under
-    `<prefix>.<left_name>` and `<prefix>.<right_name>`."""
+    `<prefix>.<left_name>` and `<prefix>.<right_name>`.  `join == "normed"`: each side's result is first divided by its root mean
+    square over the model width (`eps`) and multiplied by a weight of its own (`<prefix>.<side name>.out`)."""
 
     left: object
     right: object
@@ -256,6 +300,8 @@ class SideBySideSpec:
     left_name: str = "left"
     right_name: str = "right"
     kind: str = "side_by_side"
+    join: str = "sum"
+    eps: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -265,7 +311,8 @@ class RoutedExpertsSpec:
     renormalised over the chosen ones only if `renormalize` (a softmax score renormalised is the softmax over the chosen logits
     alone).  `router_bias` adds the tensor `<prefix>.router.b` to the logits.  `weigh` says what an expert's weight multiplies:
     its `"output"`, or its `"input"` (the expert then reads `weight * h`).  `shared` is a feed-forward that every token passes; with
-    `shared_gate` its output is scaled by the sigmoid of one more projection of the token."""
+    `shared_gate` its output is scaled by the sigmoid of one more projection of the token.  `identity` > 0: the router has that
+    many more outputs, behind the experts', which stand for experts without tensors that return what they read."""
 
     hidden: int
     intermediate: int
@@ -279,11 +326,13 @@ class RoutedExpertsSpec:
     kind: str = "routed_experts"
     router_bias: bool = False
     weigh: str = "output"
+    identity: int = 0
 
 
 @dataclass(frozen=True)
 class BlockSpec:
-    """One layer: its weight-name prefix, its two parts and the norm before each."""
+    """One layer: its weight-name prefix, its two parts and the norm before each.  `residual_scale` (parallel blocks): what the two
+    parts return is multiplied by it as it joins the residual stream."""
 
     prefix: str
     mixer: object
@@ -291,6 +340,7 @@ class BlockSpec:
     mixer_norm: NormSpec
     feed_forward_norm: Optional[NormSpec]
     kind: str = "pre_norm"
+    residual_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -381,3 +431,5 @@ class ModelSpec:
     # The embedded rows are multiplied by this as they enter the residual stream (a 32-bit stream if it is not 1); the head reads
     # the table as it is.
     embedding_scale: float = 1.0
+    # The logits are the head's product times this.
+    logit_scale: float = 1.0

@@ -82,12 +82,13 @@ _CLASS_OF = {
     "gemm_skinny": "product", "gemm_tc": "product", "attention_prepare": "attention", "attention": "attention",
     "attention_decode": "attention", "attention_prefill": "attention", "attention_prefill_tc": "attention", "argmax": "selection",
     "sample_gumbel": "selection", "store_words_host": "selection", "random_normal": "other",
-    "stream_add_norm": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
+    "stream_add_norm": "norm", "normed_pair_sum": "norm", "gated_group_norm": "norm", "gemm_simt_batched": "product", "linear_recurrence": "recurrence",
     "latent_prepare": "attention", "latent_attention": "attention", "latent_expand": "attention", "moe_route": "routing", "moe_gate_up": "experts", "moe_down": "experts", "gemm_tc_groups": "experts", "moe_sort": "routing", "moe_gather": "routing",
     "moe_combine": "routing", "diff_prepare": "attention", "diff_attention": "attention", "diff_combine": "attention", "causal_taps": "norm", "gated_add_norm": "norm",
     "side_gate": "activation", "unit_add_mix": "norm", "norm_rows": "norm", "relu_squared": "activation",
     "short_conv": "recurrence", "delta_prepare": "recurrence", "delta_rule": "recurrence", "selective_scan": "recurrence",
     "masked_prepare": "attention", "masked_attention": "attention",
+    "token_shift": "recurrence", "tanh": "activation", "channel_decay": "recurrence", "wkv": "recurrence",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
 
@@ -166,13 +167,14 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scal
                                  ctypes.c_int(table.shape[1]), ctypes.c_int(table.shape[0]), _stream()), "embedding")
 
 
-def rms_norm(values, weight, eps: float, out, rows=None, branch=None) -> None:
+def rms_norm(values, weight, eps: float, out, rows=None, branch=None, groups: int = 1, branch_scale: float = 1.0) -> None:
     """`out[i] = norm(round(values[r] + branch[r])) * weight`, `r = rows[i]` or `i`; `values` is not changed.
 
     Where `values` is a 32-bit stream and the output is not, or there are two branches (a tuple), the sum is taken in
-    32-bit (`values[r] + (a[r] + b[r])`) and only the output is rounded."""
-    if isinstance(branch, (tuple, list)) or values.dtype != out.dtype:
-        return stream_add_norm(values, branch, weight, eps, out, rows=rows, update=False)
+    32-bit (`values[r] + branch_scale * (a[r] + b[r])`) and only the output is rounded; a norm over `groups` > 1 pieces of the row,
+    or a scale on the branches, needs the 32-bit stream as well."""
+    if isinstance(branch, (tuple, list)) or values.dtype != out.dtype or groups != 1 or branch_scale != 1.0:
+        return stream_add_norm(values, branch, weight, eps, out, rows=rows, update=False, groups=groups, branch_scale=branch_scale)
     _on_device(values, weight, out, rows, branch)
     width = values.shape[-1]
     _f32_vector(weight, width, "the norm weight")
@@ -189,11 +191,11 @@ def rms_norm(values, weight, eps: float, out, rows=None, branch=None) -> None:
                                 ctypes.c_int(count), ctypes.c_int(width), ctypes.c_float(eps), _stream()), "rms_norm")
 
 
-def add_rms_norm(branch, residual, weight, eps: float, out) -> None:
+def add_rms_norm(branch, residual, weight, eps: float, out, groups: int = 1, branch_scale: float = 1.0) -> None:
     """`residual = round(residual + branch)` in place; `out = norm(residual) * weight`.  A 32-bit residual beside an output
-    of another dtype, or two branches (a tuple), go to `stream_add_norm`."""
-    if isinstance(branch, (tuple, list)) or residual.dtype != out.dtype:
-        return stream_add_norm(residual, branch, weight, eps, out, update=True)
+    of another dtype, two branches (a tuple), a norm in `groups` pieces or a scale on the branches go to `stream_add_norm`."""
+    if isinstance(branch, (tuple, list)) or residual.dtype != out.dtype or groups != 1 or branch_scale != 1.0:
+        return stream_add_norm(residual, branch, weight, eps, out, update=True, groups=groups, branch_scale=branch_scale)
     _on_device(branch, residual, weight, out)
     width = residual.shape[-1]
     _f32_vector(weight, width, "the norm weight")
@@ -206,10 +208,15 @@ def add_rms_norm(branch, residual, weight, eps: float, out) -> None:
            "add_rms_norm")
 
 
-def stream_add_norm(stream, branches, weight, eps: float, out, rows=None, update: bool = True) -> None:
-    """A residual stream kept in 32-bit: `sum = stream[r] + (a[r] + b[r])` in 32-bit for up to two branches of any dtype
-    (`branches`: None, a tensor or a tuple of one or two), `r = rows[i]` or `i`; with `update` (no `rows` then) the sum
-    replaces `stream[r]`; `out[i] = sum / sqrt(mean(sum^2) + eps) * weight`, rounded once to the output's dtype."""
+NORM_MAX_GROUPS = 64
+
+
+def stream_add_norm(stream, branches, weight, eps: float, out, rows=None, update: bool = True, groups: int = 1, branch_scale: float = 1.0) -> None:
+    """A residual stream kept in 32-bit: `sum = stream[r] + branch_scale * (a[r] + b[r])` in 32-bit for up to two branches of any
+    dtype (`branches`: None, a tensor or a tuple of one or two), `r = rows[i]` or `i`; with `update` (no `rows` then) the sum
+    replaces `stream[r]`; `out[i] = sum / sqrt(mean(sum^2) + eps) * weight`, rounded once to the output's dtype.  With `groups` > 1
+    the row is cut into that many equal consecutive pieces, each divided by its own root mean square."""
+    _require(1 <= groups <= NORM_MAX_GROUPS and stream.shape[-1] % groups == 0, f"the groups (at most {NORM_MAX_GROUPS}) must divide the width")
     if branches is None:
         branches = ()
     elif not isinstance(branches, (tuple, list)):
@@ -234,7 +241,22 @@ def stream_add_norm(stream, branches, weight, eps: float, out, rows=None, update
     _check(library.tau_stream_add_norm(_code(out), _pointer(stream), _pointer(first), ctypes.c_int(_code(first) if first is not None else 0),
                                        _pointer(second), ctypes.c_int(_code(second) if second is not None else 0), _pointer(rows), _pointer(weight),
                                        _pointer(out), ctypes.c_int(count), ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_int(1 if update else 0),
-                                       _stream()), "stream_add_norm")
+                                       ctypes.c_int(groups), ctypes.c_float(branch_scale), _stream()), "stream_add_norm")
+
+
+def normed_pair_sum(left, right, left_weight, right_weight, eps: float, left_scale: float, right_scale: float, out) -> None:
+    """`out = left_scale * left / rms(left) * left_weight + right_scale * right / rms(right) * right_weight`, each root mean square
+    over the whole row (eps inside the root); everything float32 [rows, width]."""
+    _on_device(left, right, left_weight, right_weight, out)
+    rows, width = left.shape
+    for tensor in (left, right, out):
+        _require(tensor.dtype == torch.float32 and tensor.shape == (rows, width) and tensor.is_contiguous(), "both results and the output must be contiguous float32 [rows, width]")
+    _f32_vector(left_weight, width, "the left weight")
+    _f32_vector(right_weight, width, "the right weight")
+    library = build.load_library("stream32.cu")
+    _check(library.tau_normed_pair_sum(_pointer(left), _pointer(right), _pointer(left_weight), _pointer(right_weight), _pointer(out), ctypes.c_int(rows),
+                                       ctypes.c_int(width), ctypes.c_float(eps), ctypes.c_float(left_scale), ctypes.c_float(right_scale), _stream()),
+           "normed_pair_sum")
 
 
 def gated_group_norm(values, weight, gate, out, groups: int, eps: float, normalize: bool, silu_gate: bool = False) -> None:
@@ -412,7 +434,7 @@ def gemm_tc_groups(values, weights, out, bounds, gated: bool = False) -> None:
     groups, features = weights.shape[0], weights.shape[1]
     _require(weights.shape[2] == depth and weights.is_contiguous() and out.shape == (rows, features // 2 if gated else features),
              "shapes must be [M,K] x [G,N,K] -> [M,N]")
-    _require(len(bounds) == groups + 1 and bounds[0] == 0 and bounds[-1] == rows, "bounds must run from 0 to the number of rows")
+    _require(len(bounds) == groups + 1 and bounds[0] == 0 and bounds[-1] <= rows, "bounds must start at 0 and end within the rows")
     _require(values.dtype == weights.dtype == torch.bfloat16 and out.dtype in (torch.bfloat16, torch.float32) and (not gated or out.dtype == torch.bfloat16),
              "inputs must be bfloat16 and the output bfloat16 or float32 (bfloat16 for a gated product)")
     _require(_tc_fits(values, weights[0], out) and (not gated or features % 16 == 0), "needs K % 8 == 0 and 16-byte aligned rows")
@@ -1146,34 +1168,42 @@ def short_conv(x, weight, bias, state, step, out, silu: bool = True, update: boo
 DELTA_MAX_KEY_DIM = 512
 
 
-def delta_prepare(rows, q_offset: int, k_offset: int, pre, a_log, dt_bias, gates, kq, n_heads: int, n_key_heads: int, key_dim: int) -> None:
+def delta_prepare(rows, q_offset: int, k_offset: int, pre, a_log, dt_bias, gates, kq, n_heads: int, n_key_heads: int, key_dim: int, channel=None) -> None:
     """In place on `rows` (float32 [tokens, width]): the queries (`n_key_heads * key_dim` columns from `q_offset`) and keys (from
     `k_offset`) become unit vectors per head, `x / sqrt(sum(x^2) + 1e-6)`, the queries also times `key_dim ** -0.5`.
     `kq` [tokens, n_key_heads] receives `k . q` of the results.  `pre` float32 [tokens, 2 * n_heads] holds per value head the
     pre-activation of beta, then of the decay's step; `gates` [tokens, n_heads, 2] receives
-    `(exp(-exp(a_log) * softplus(step + dt_bias)), sigmoid(beta))`."""
-    _on_device(rows, pre, a_log, dt_bias, gates, kq)
+    `(exp(-exp(a_log) * softplus(step + dt_bias)), sigmoid(beta))`.  With `channel` (float32 [tokens, n_heads * key_dim]: the
+    pre-activations of a decay per head and key channel) `pre` holds beta's alone ([tokens, n_heads]), `dt_bias` is as wide as
+    `channel`, and `channel` is replaced by `exp(-exp(a_log[head]) * softplus(channel + dt_bias))`."""
+    _on_device(rows, pre, a_log, dt_bias, gates, kq, channel)
     tokens = rows.shape[0]
     _require(rows.dtype == torch.float32 and rows.stride(1) == 1 and max(q_offset, k_offset) + n_key_heads * key_dim <= rows.shape[1], "rows must be float32 and hold q and k")
-    _require(pre.dtype == torch.float32 and pre.shape == (tokens, 2 * n_heads) and pre.is_contiguous(), "the gates' pre-activations must be float32 [tokens, 2 * heads]")
+    _require(pre.dtype == torch.float32 and pre.dim() == 2 and pre.shape[0] == tokens and pre.shape[1] >= (1 if channel is not None else 2) * n_heads
+             and pre.stride(1) == 1, "the gates' pre-activations must be float32 [tokens, 2 * heads] (beta's alone beside a decay per channel)")
     _f32_vector(a_log, n_heads, "A_log")
-    _f32_vector(dt_bias, n_heads, "dt_bias")
+    _f32_vector(dt_bias, n_heads * (key_dim if channel is not None else 1), "dt_bias")
+    if channel is not None:
+        _require(channel.dtype == torch.float32 and channel.shape == (tokens, n_heads * key_dim) and channel.is_contiguous(), "the decays must be float32 [tokens, heads * key_dim]")
     _require(gates.dtype == torch.float32 and gates.shape == (tokens, n_heads, 2) and gates.is_contiguous(), "gates must be float32 [tokens, heads, 2]")
     _require(kq.dtype == torch.float32 and kq.shape == (tokens, n_key_heads) and kq.is_contiguous(), "kq must be float32 [tokens, key heads]")
     _require(1 <= key_dim <= DELTA_MAX_KEY_DIM and n_heads % n_key_heads == 0, f"key_dim must lie between 1 and {DELTA_MAX_KEY_DIM}, and the key heads divide the heads")
     library = build.load_library("delta_rule.cu", (f"TAU_KEY_DIM={key_dim}",))
     _check(library.tau_delta_prepare(_pointer(rows), ctypes.c_longlong(rows.stride(0)), ctypes.c_int(q_offset), ctypes.c_int(k_offset), _pointer(pre),
-                                     _pointer(a_log), _pointer(dt_bias), _pointer(gates), _pointer(kq), ctypes.c_int(tokens), ctypes.c_int(n_heads),
+                                     ctypes.c_int(pre.stride(0)), _pointer(a_log), _pointer(dt_bias), _pointer(gates), _pointer(kq), _pointer(channel), ctypes.c_int(tokens), ctypes.c_int(n_heads),
                                      ctypes.c_int(n_key_heads), ctypes.c_float(key_dim ** -0.5), _stream()), "delta_prepare")
 
 
 def delta_rule(rows, q_offset: int, k_offset: int, v_offset: int, gates, kq, state, cu_seqlens, seq_slot, out, n_heads: int, n_key_heads: int,
-               key_dim: int, value_dim: int) -> None:
+               key_dim: int, value_dim: int, channel=None) -> None:
     """Advances the gated delta rule of every (sequence, head) over the sequence's new tokens: `S <- g S; u = beta (v - S^T k);
     S <- S + k u^T; o = S^T q`.  `rows` as `delta_prepare` left them, with the values (`n_heads * value_dim` columns) from
     `v_offset`; `gates` [tokens, n_heads, 2] = (g, beta); `kq` [tokens, n_key_heads]; `state` float32 [slots, n_heads * value_dim *
-    key_dim], updated in place; `out` float32 [tokens, n_heads * value_dim]."""
-    _on_device(rows, gates, kq, state, cu_seqlens, seq_slot, out)
+    key_dim], updated in place; `out` float32 [tokens, n_heads * value_dim].  `channel` (float32 [tokens, n_heads * key_dim], as
+    `delta_prepare` left it): g is that vector over the state's rows instead of the head's one number."""
+    _on_device(rows, gates, kq, state, cu_seqlens, seq_slot, out, channel)
+    if channel is not None:
+        _require(channel.dtype == torch.float32 and channel.shape == (rows.shape[0], n_heads * key_dim) and channel.is_contiguous(), "the decays must be float32 [tokens, heads * key_dim]")
     tokens = rows.shape[0]
     _require(rows.dtype == torch.float32 and rows.stride(1) == 1 and v_offset + n_heads * value_dim <= rows.shape[1], "rows must be float32 and hold q, k and v")
     _require(gates.dtype == torch.float32 and gates.shape == (tokens, n_heads, 2) and gates.is_contiguous(), "gates must be float32 [tokens, heads, 2]")
@@ -1188,7 +1218,7 @@ def delta_rule(rows, q_offset: int, k_offset: int, v_offset: int, gates, kq, sta
     _require(cu_seqlens.numel() == n_seqs + 1, "one run per sequence")
     library = build.load_library("delta_rule.cu", (f"TAU_KEY_DIM={key_dim}",))
     _check(library.tau_delta_rule(_pointer(rows), ctypes.c_longlong(rows.stride(0)), ctypes.c_int(q_offset), ctypes.c_int(k_offset), ctypes.c_int(v_offset),
-                                  _pointer(gates), _pointer(kq), _pointer(state), ctypes.c_longlong(state.stride(0)), _pointer(cu_seqlens), _pointer(seq_slot),
+                                  _pointer(gates), _pointer(kq), _pointer(channel), _pointer(state), ctypes.c_longlong(state.stride(0)), _pointer(cu_seqlens), _pointer(seq_slot),
                                   _pointer(out), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(n_key_heads), ctypes.c_int(value_dim), _stream()),
            "delta_rule")
 
@@ -1229,18 +1259,23 @@ MASKED_MAX_VALUE_DIM = 512
 
 
 def masked_prepare(projected, q_weight, k_weight, eps: float, frequency, rotary_dim: int, magnitude: float, queries, rows, positions, token_seq,
-                   page_rows, n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_rows: bool = True, value_pages=None) -> None:
+                   page_rows, n_heads: int, n_kv_heads: int, dim: int, vdim: int, write_rows: bool = True, value_pages=None,
+                   temperature=None) -> None:
     """`projected` [tokens, >= n_heads * dim + n_kv_heads * (dim + vdim)] holds queries, keys and values side by side.  With weights
     (float32 [n_heads * dim] and [n_kv_heads * dim]) the queries, and the keys, are divided by the root mean square over their
     whole projection (eps inside the root) and multiplied by the weight.  In every head element `i` of the first `rotary_dim` is
     turned together with element `i + rotary_dim / 2` by `position * frequency[i]`, sine and cosine times `magnitude`.  Queries go
     to `queries` [tokens, n_heads, dim]; with `write_rows` keys and values go to the token's row of the cache pages `rows`
     [pages, 64, n_kv_heads * (dim + vdim)] as [keys of all heads | values], or, with `value_pages`, to pages of ordinary heads:
-    keys to `rows` [pages, n_kv_heads, 64, dim], values to `value_pages` [pages, n_kv_heads, 64, vdim]."""
+    keys to `rows` [pages, n_kv_heads, 64, dim], values to `value_pages` [pages, n_kv_heads, 64, vdim].  Without `write_rows` the
+    projection need hold the queries alone.  `temperature` = (coef, every): the query at position p is multiplied by
+    `1 + coef * ln(floor((p + 1) / every) + 1)`."""
     _on_device(projected, q_weight, k_weight, frequency, queries, rows, positions, token_seq, page_rows, value_pages)
     tokens = projected.shape[0]
     row_width = n_kv_heads * (dim + vdim)
-    _require(projected.shape[1] >= n_heads * dim + row_width and projected.stride(1) == 1, "the projection is too narrow")
+    _require(projected.shape[1] >= n_heads * dim + (row_width if write_rows else 0) and projected.stride(1) == 1, "the projection is too narrow")
+    coef, every = (0.0, 0) if temperature is None else (float(temperature[0]), int(temperature[1]))
+    _require(every >= 0, "the temperature's period must be positive")
     _require(queries.shape == (tokens, n_heads, dim) and queries.is_contiguous() and queries.dtype == projected.dtype, "queries must be [tokens, n_heads, dim]")
     _f32_vector(q_weight, n_heads * dim, "the query norm weight")
     _f32_vector(k_weight, n_kv_heads * dim, "the key norm weight")
@@ -1258,7 +1293,7 @@ def masked_prepare(projected, q_weight, k_weight, eps: float, frequency, rotary_
         _pointer(frequency if rotary_dim else None), ctypes.c_int(rotary_dim), ctypes.c_float(magnitude), _pointer(queries), _pointer(rows if write_rows else None),
         _pointer(value_pages if write_rows else None), _pointer(positions), _pointer(token_seq), _pointer(page_rows), ctypes.c_int(page_rows.shape[1] if write_rows else 0), ctypes.c_int(PAGE_TOKENS),
         ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_int(1 if write_rows else 0),
-        _stream()), "masked_prepare")
+        ctypes.c_float(coef), ctypes.c_int(every), _stream()), "masked_prepare")
 
 
 def _require_masked_pages(rows, value_pages, dtype, n_kv_heads: int, dim: int, vdim: int) -> None:
@@ -1270,15 +1305,27 @@ def _require_masked_pages(rows, value_pages, dtype, n_kv_heads: int, dim: int, v
 
 
 def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim: int, scale: float, window: int = 0, chunk: int = 0, sink: bool = False,
-                     out_scale: float = 1.0, value_pages=None, staged: bool = False) -> None:
+                     out_scale: float = 1.0, value_pages=None, staged: bool = False, distance=None, sigmoid_weights: bool = False, head_offset=None,
+                     gate=None, gate_per_head: bool = False) -> None:
     """Causal softmax attention of every token over the cached rows of its sequence: within `window` positions (if not 0), or
     within the token's own chunk of `chunk` positions counted from position 0 (if not 0); with `sink` the softmax's denominator has
     one added.  `out` [tokens, n_heads * vdim] (rows any distance apart) receives the result times `out_scale`.  Scores, weights
     and sums are 32-bit.  The cache is `rows`, or `rows` and `value_pages` in the layout of ordinary heads (see `masked_prepare`).
     `staged` (meant for steps of single tokens) asks for the kernel that stages tiles of the cache in shared memory and shares them
-    among the heads of a key/value head; sizes that it does not serve take the other kernel."""
-    _on_device(queries, rows, out, page_rows, value_pages)
+    among the heads of a key/value head; sizes that it does not serve take the other kernel.  `distance` (float32 [n_heads, 2] =
+    (r1, r2)): `r1 * ln(1 + r2 * (i - j))` is taken off the score of key j for the query at i.  `sigmoid_weights`: instead of a
+    softmax every visible key weighs `sigmoid(score + head_offset[head])` (float32 [n_heads] or None), not normalised.  `gate`
+    ([tokens, n_heads] with `gate_per_head`, else [tokens, n_heads * vdim]; the queries' dtype; rows any distance apart): the result
+    is multiplied by its sigmoid."""
+    _on_device(queries, rows, out, page_rows, value_pages, distance, head_offset, gate)
     tokens, n_heads, dim = queries.shape
+    if distance is not None:
+        _require(distance.dtype == torch.float32 and distance.shape == (n_heads, 2) and distance.is_contiguous(), "the distance numbers must be float32 [heads, 2]")
+    _f32_vector(head_offset, n_heads, "the heads' offsets")
+    _require(not (sigmoid_weights and sink), "sigmoid weights have no denominator for a sink to join")
+    if gate is not None:
+        _require(gate.dtype == queries.dtype and gate.shape == (tokens, n_heads if gate_per_head else n_heads * vdim) and gate.stride(1) == 1,
+                 "the gate must be [tokens, heads] or [tokens, heads * vdim] in the queries' dtype")
     _require(queries.is_contiguous() and out.shape == (tokens, n_heads * vdim) and out.stride(1) == 1 and out.dtype == queries.dtype == rows.dtype,
              "queries must be [tokens, n_heads, dim] and the output [tokens, n_heads * vdim]")
     _require_masked_pages(rows, value_pages, queries.dtype, n_kv_heads, dim, vdim)
@@ -1290,7 +1337,69 @@ def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim:
         _code(queries), _pointer(queries), _pointer(rows), _pointer(value_pages), _pointer(out), ctypes.c_longlong(out.stride(0)), _pointer(step.positions), _pointer(step.token_seq),
         _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk), ctypes.c_int(1 if sink else 0),
-        ctypes.c_float(out_scale), ctypes.c_int(1 if staged else 0), _stream()), "masked_attention")
+        ctypes.c_float(out_scale), ctypes.c_int(1 if staged else 0), _pointer(distance), ctypes.c_int(1 if sigmoid_weights else 0), _pointer(head_offset),
+        _pointer(gate), ctypes.c_longlong(0 if gate is None else gate.stride(0)), ctypes.c_int(1 if gate_per_head else 0), _stream()), "masked_attention")
+
+
+# ---------------------------------------------------------------------------- a matrix state with a decay per key channel and a bonus
+WKV_MAX_KEY_DIM = 512
+
+
+def token_shift(x, mu, last, step, out, update: bool = True) -> None:
+    """`out[s, t] = x[t] + (before[t] - x[t]) * mu[s]` for every vector `mu[s]` (float32 [mixes, width]), `before[t]` being the row of
+    the token before in its sequence: `x[t - 1]` inside a run, `last[slot]` (float32 [slots, width], zeros when the sequence starts)
+    for a run's first token.  `out` [mixes, tokens, width] of `x`'s dtype.  With `update`, `last[slot]` then becomes the run's last
+    row (a second launch, or the same one where every sequence brings one token)."""
+    _on_device(x, mu, last, out)
+    tokens, width = x.shape
+    mixes = mu.shape[0]
+    _require(x.is_contiguous() and out.shape == (mixes, tokens, width) and out.dtype == x.dtype and out.is_contiguous(), "the output must be [mixes, tokens, width]")
+    _require(mu.dtype == torch.float32 and mu.shape == (mixes, width) and mu.is_contiguous(), "the mixes must be float32 [mixes, width]")
+    _require(last.dtype == torch.float32 and last.dim() == 2 and last.shape[1] == width and last.is_contiguous(), "the kept inputs must be float32 [slots, width]")
+    single = bool(getattr(step, "all_single", False)) and tokens == step.n_seqs
+    library = build.load_library("wkv.cu", ("TAU_KEY_DIM=64",))      # the shift does not depend on the key width
+    _check(library.tau_token_shift(_code(x), _pointer(x), _pointer(mu), _pointer(last), _pointer(step.token_seq), _pointer(step.cu_seqlens), _pointer(step.seq_slot),
+                                   _pointer(out), ctypes.c_int(tokens), ctypes.c_int(step.n_seqs), ctypes.c_int(width), ctypes.c_int(mixes),
+                                   ctypes.c_int(1 if update else 0), ctypes.c_int(1 if single else 0), _stream()), "token_shift", 2 if update and not single else 1)
+
+
+def tanh_(values) -> None:
+    """`values = tanh(values)` in place."""
+    _on_device(values)
+    _require(values.is_contiguous(), "the values must be contiguous")
+    library = build.load_library("wkv.cu", ("TAU_KEY_DIM=64",))
+    _check(library.tau_tanh(_code(values), _pointer(values), ctypes.c_longlong(values.numel()), _stream()), "tanh")
+
+
+def channel_decay(values, offset) -> None:
+    """In place on float32 [rows, width]: `exp(-exp(values + offset))`, `offset` float32 [width]."""
+    _on_device(values, offset)
+    rows, width = values.shape
+    _require(values.dtype == torch.float32 and values.is_contiguous(), "the pre-activations must be contiguous float32")
+    _f32_vector(offset, width, "the decays' offset")
+    library = build.load_library("wkv.cu", ("TAU_KEY_DIM=64",))
+    _check(library.tau_channel_decay(_pointer(values), _pointer(offset), ctypes.c_longlong(rows), ctypes.c_int(width), _stream()), "channel_decay")
+
+
+def wkv(r, k, v, w, bonus, state, cu_seqlens, seq_slot, out, n_heads: int, key_dim: int, value_dim: int) -> None:
+    """Per (sequence, head) over the sequence's new tokens: `o = (S + diag(bonus) k v^T)^T r`, then `S <- diag(w) S + k v^T`.
+    `r`, `k`, `w` float32 [tokens, n_heads * key_dim], `v` and `out` float32 [tokens, n_heads * value_dim], `bonus` float32
+    [n_heads, key_dim], `state` float32 [slots, n_heads * value_dim * key_dim], updated in place."""
+    _on_device(r, k, v, w, bonus, state, cu_seqlens, seq_slot, out)
+    tokens = r.shape[0]
+    for tensor, width, what in ((r, key_dim, "r"), (k, key_dim, "k"), (w, key_dim, "w"), (v, value_dim, "v"), (out, value_dim, "the output")):
+        _require(tensor.dtype == torch.float32 and tensor.shape == (tokens, n_heads * width) and tensor.is_contiguous(), f"{what} must be contiguous float32 [tokens, heads * width]")
+    _require(bonus.dtype == torch.float32 and bonus.shape == (n_heads, key_dim) and bonus.is_contiguous(), "the bonus must be float32 [heads, key_dim]")
+    _require(state.dtype == torch.float32 and state.dim() == 2 and state.is_contiguous() and state.shape[1] == n_heads * value_dim * key_dim,
+             f"the state must be float32 [slots, {n_heads * value_dim * key_dim}]")
+    _require(1 <= key_dim <= WKV_MAX_KEY_DIM, f"key_dim must lie between 1 and {WKV_MAX_KEY_DIM}")
+    _int_vector(cu_seqlens, "cu_seqlens")
+    _int_vector(seq_slot, "seq_slot")
+    n_seqs = seq_slot.numel()
+    _require(cu_seqlens.numel() == n_seqs + 1, "one run per sequence")
+    library = build.load_library("wkv.cu", (f"TAU_KEY_DIM={key_dim}",))
+    _check(library.tau_wkv(_pointer(r), _pointer(k), _pointer(v), _pointer(w), _pointer(bonus), _pointer(state), ctypes.c_longlong(state.stride(0)),
+                           _pointer(cu_seqlens), _pointer(seq_slot), _pointer(out), ctypes.c_int(n_seqs), ctypes.c_int(n_heads), ctypes.c_int(value_dim), _stream()), "wkv")
 
 
 # ---------------------------------------------------------------------------- routed experts
@@ -1320,6 +1429,7 @@ def moe_route(hidden, router, correction, shared_gate_weight, chosen, weights, s
 
 
 def moe_gate_up(hidden, gate_up, chosen, inner, interleave: int = 0, input_weights=None) -> None:
+    # A pair whose expert number is not below `gate_up.shape[0]` chose an identity expert: its place of `inner` is left unwritten.
     """`inner[token, place] = silu(gate_e @ x) * (up_e @ x)` with `e = chosen[token, place]` and `x = h`, or
     `x = input_weights[token, place] * h` (float32 [tokens, top]; the weight multiplies the two products' 32-bit sums); `gate_up`
     [experts, 2 * I, width] holds each expert's gate rows, then its up rows, or with `interleave` groups of that many gate rows
@@ -1337,14 +1447,17 @@ def moe_gate_up(hidden, gate_up, chosen, inner, interleave: int = 0, input_weigh
         _require(input_weights.shape == (tokens, top) and input_weights.dtype == torch.float32 and input_weights.is_contiguous(), "input weights must be float32 [tokens, top]")
     library = build.load_library("moe.cu")
     _check(library.tau_moe_gate_up(_code(hidden), _pointer(hidden), _pointer(gate_up), _pointer(chosen), _pointer(input_weights), _pointer(inner), ctypes.c_int(tokens),
-                                   ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top), ctypes.c_int(interleave), _stream()), "moe_gate_up")
+                                   ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top), ctypes.c_int(interleave), ctypes.c_int(gate_up.shape[0]), _stream()), "moe_gate_up")
 
 
-def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out) -> None:
+def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out, hidden=None) -> None:
     """`out[token] = sum_place weights[token, place] * (down_e @ inner[token, place]) + shared_gate[token] * shared_out[token]`,
     float32 [tokens, width]; `down` [experts, width, I]; `weights` (None: 1), `shared_out` (the activations' dtype) and
-    `shared_gate` (float32 [tokens]; None: 1) are optional."""
-    _on_device(inner, down, chosen, weights, shared_out, shared_gate, out)
+    `shared_gate` (float32 [tokens]; None: 1) are optional.  A place whose expert number is not below `down.shape[0]` chose an
+    identity expert and adds its weight times `hidden[token]` (what the experts read, [tokens, width]; None: there are no such experts)."""
+    _on_device(inner, down, chosen, weights, shared_out, shared_gate, out, hidden)
+    if hidden is not None:
+        _require(hidden.shape == out.shape and hidden.dtype == inner.dtype and hidden.is_contiguous(), "the experts' input must be [tokens, width]")
     tokens, top, size = inner.shape
     width = down.shape[1]
     _require(inner.is_contiguous() and down.is_contiguous() and inner.dtype == down.dtype and down.shape[2] == size, "down must be [experts, width, I]")
@@ -1358,7 +1471,7 @@ def moe_down(inner, down, chosen, weights, shared_out, shared_gate, out) -> None
     library = build.load_library("moe.cu")
     _check(library.tau_moe_down(_code(inner), _pointer(inner), _pointer(down), _pointer(chosen), _pointer(weights), _pointer(shared_out),
                                 _pointer(shared_gate), _pointer(out), ctypes.c_int(tokens), ctypes.c_int(width), ctypes.c_int(size), ctypes.c_int(top),
-                                _stream()), "moe_down")
+                                _pointer(hidden), ctypes.c_int(down.shape[0]), _stream()), "moe_down")
 
 
 def moe_sort(chosen, experts: int, offsets, order, position) -> None:
@@ -1387,10 +1500,14 @@ def moe_gather(hidden, order, top: int, gathered, input_weights=None) -> None:
                                   ctypes.c_int(top), _stream()), "moe_gather")
 
 
-def moe_combine(rows, position, weights, shared_out, shared_gate, out) -> None:
+def moe_combine(rows, position, weights, shared_out, shared_gate, out, chosen=None, hidden=None, real_experts: int = 0) -> None:
     """`out[token] = sum_place weights[token, place] * rows[position[token, place]] + shared_gate[token] * shared_out[token]`;
-    `rows` float32 [pairs, width], `out` float32 [tokens, width]; `weights` None: 1."""
-    _on_device(rows, position, weights, shared_out, shared_gate, out)
+    `rows` float32 [pairs, width], `out` float32 [tokens, width]; `weights` None: 1.  With `chosen` ([tokens, top] int32) a place
+    whose expert number is not below `real_experts` chose an identity expert: `hidden[token]` stands for its row."""
+    _on_device(rows, position, weights, shared_out, shared_gate, out, chosen, hidden)
+    if chosen is not None:
+        _require(hidden is not None and hidden.shape == out.shape and hidden.is_contiguous() and chosen.dtype == torch.int32 and chosen.numel() == position.numel()
+                 and chosen.is_contiguous() and (shared_out is None or shared_out.dtype == hidden.dtype), "identity experts need the experts' input [tokens, width]")
     tokens, width = out.shape
     top = position.numel() // tokens
     _require(rows.dtype == torch.float32 == out.dtype and rows.shape == (tokens * top, width) and rows.is_contiguous() and out.is_contiguous(),
@@ -1401,9 +1518,10 @@ def moe_combine(rows, position, weights, shared_out, shared_gate, out) -> None:
     if shared_out is not None:
         _require(shared_out.shape == (tokens, width) and shared_out.is_contiguous(), "the shared output must be [tokens, width]")
     library = build.load_library("moe.cu")
-    _check(library.tau_moe_combine(_code(shared_out) if shared_out is not None else 0, _pointer(rows), _pointer(position), _pointer(weights),
+    code = _code(hidden) if chosen is not None else _code(shared_out) if shared_out is not None else 0
+    _check(library.tau_moe_combine(code, _pointer(rows), _pointer(position), _pointer(weights),
                                    _pointer(shared_out), _pointer(shared_gate), _pointer(out), ctypes.c_int(tokens), ctypes.c_int(width),
-                                   ctypes.c_int(top), _stream()), "moe_combine")
+                                   ctypes.c_int(top), _pointer(chosen), _pointer(hidden if chosen is not None else None), ctypes.c_int(real_experts), _stream()), "moe_combine")
 
 
 # ---------------------------------------------------------------------------- random weights

@@ -5,7 +5,12 @@
 //   * a query at position i sees key j <= i if j > i - window (`window` > 0), or if j lies in i's chunk, floor(j / chunk) ==
 //     floor(i / chunk) (`chunk` > 0; chunks are counted from position 0 of the sequence), or always (both 0);
 //   * `sink`: the denominator of the softmax has exp(0) added (a key with score 0 and no value);
-//   * the result is multiplied by `out_scale` before its one rounding; output rows may lie any distance apart.
+//   * the result is multiplied by `out_scale` before its one rounding; output rows may lie any distance apart;
+//   * `distance` (two numbers r1, r2 per head): r1 * ln(1 + r2 * (i - j)) is taken off the score of key j for the query at i;
+//   * `sigmoid_weights`: no softmax; a visible key weighs sigmoid(score + head_offset[head]) and the weights are not normalised;
+//   * `gate`: the result is multiplied by sigmoid(gate), one number per (token, head) or one per element of the head's result;
+//   * prepare may multiply the query at position p by 1 + coef * ln(floor((p + 1) / every) + 1) (a temperature that grows with the
+//     position), and may be asked for the queries alone (a layer that reads the keys and values another layer cached).
 //
 //   prepare:    q and k divided by the root mean square over the WHOLE projection (all heads together; eps inside the root) and
 //               multiplied by a weight of that size (or left as they are without weights); then in every head the first `rotary`
@@ -27,7 +32,7 @@ __global__ void __launch_bounds__(kWarps * 32)
 masked_prepare_kernel(const T* __restrict__ projected, long long projected_stride, const float* __restrict__ q_weight, const float* __restrict__ k_weight,
                       float eps, const float* __restrict__ frequency, int rotary, float magnitude, T* __restrict__ queries, T* __restrict__ rows,
                       T* __restrict__ value_pages, const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
-                      int page_tokens, int heads, int kv_heads, int dim, int vdim, int write_rows) {
+                      int page_tokens, int heads, int kv_heads, int dim, int vdim, int write_rows, float temperature_coef, int temperature_every) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ float2 turns[];
@@ -59,6 +64,7 @@ masked_prepare_kernel(const T* __restrict__ projected, long long projected_strid
         }
         k_inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(k_width) + eps);
     }
+    if (temperature_every > 0) q_inverse *= 1.0f + temperature_coef * logf(static_cast<float>((position + 1) / temperature_every + 1));
     __syncthreads();      // the turns are complete
     // Where the token's keys and values go: head `g`'s key at row + g * key_head_stride, its value at value_row + g * value_head_stride.
     T* row = nullptr;
@@ -115,7 +121,9 @@ template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
 masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ rows, const T* __restrict__ value_pages, T* __restrict__ out, long long out_stride,
                         const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows, int page_stride,
-                        int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale) {
+                        int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale,
+                        const float* __restrict__ distance, int sigmoid_weights, const float* __restrict__ head_offset, const T* __restrict__ gate,
+                        long long gate_stride, int gate_per_head) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ float shared[];
@@ -144,6 +152,8 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
     if (window > 0 && position - window + 1 > 0) first_key = position - window + 1;
     if (chunk > 0) first_key = position / chunk * chunk;
     float top = sink ? 0.0f : -INFINITY, sum = sink ? 1.0f : 0.0f;       // the sink: a weight of exp(0 - top) that carries no value
+    const float far = distance ? distance[2 * head] : 0.0f, reach = distance ? distance[2 * head + 1] : 0.0f;
+    const float offset = head_offset ? head_offset[head] : 0.0f;
     float acc[kMaxOwned];
 #pragma unroll
     for (int i = 0; i < kMaxOwned; ++i) acc[i] = 0.0f;
@@ -164,14 +174,20 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
             }
             if (column < dim) a = fmaf(query[column], to_float(k[column]), a);
             score = a + b;
+            if (distance) score -= far * log1pf(reach * static_cast<float>(position - key));
         }
-        const float new_top = fmaxf(top, warp_max(score));       // finite: the block holds at least one key
-        const float p = valid ? expf(score - new_top) : 0.0f;
-        const float keep = expf(top - new_top);                   // exp(-inf) = 0 the first time without a sink
-        sum = sum * keep + warp_sum(p);
-        top = new_top;
+        float p;
+        if (sigmoid_weights) {
+            p = valid ? 1.0f / (1.0f + expf(-(score + offset))) : 0.0f;
+        } else {
+            const float new_top = fmaxf(top, warp_max(score));       // finite: the block holds at least one key
+            p = valid ? expf(score - new_top) : 0.0f;
+            const float keep = expf(top - new_top);                   // exp(-inf) = 0 the first time without a sink
+            sum = sum * keep + warp_sum(p);
+            top = new_top;
 #pragma unroll
-        for (int i = 0; i < kMaxOwned; ++i) acc[i] *= keep;
+            for (int i = 0; i < kMaxOwned; ++i) acc[i] *= keep;
+        }
         const int count = position - base + 1 < 32 ? position - base + 1 : 32;
         for (int j = 0; j < count; ++j) {
             const float w = __shfl_sync(0xffffffffu, p, j);
@@ -183,11 +199,16 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
             }
         }
     }
-    const float factor = out_scale / sum;
+    const float factor = sigmoid_weights ? out_scale : out_scale / sum;
+    const T* gates = gate ? gate + static_cast<size_t>(token) * gate_stride + (gate_per_head ? head : head * vdim) : nullptr;
 #pragma unroll
     for (int i = 0; i < kMaxOwned; ++i) {
         const int column = lane + 32 * i;
-        if (column < vdim) out[static_cast<size_t>(token) * out_stride + head * vdim + column] = from_float<T>(acc[i] * factor);
+        if (column < vdim) {
+            float value = acc[i] * factor;
+            if (gates) value /= 1.0f + expf(-to_float(gates[gate_per_head ? 0 : column]));
+            out[static_cast<size_t>(token) * out_stride + head * vdim + column] = from_float<T>(value);
+        }
     }
 }
 
@@ -226,7 +247,8 @@ __global__ void __launch_bounds__(kStagedWarps * 32)
 masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restrict__ rows, const T* __restrict__ value_pages, T* __restrict__ out,
                                long long out_stride, const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows,
                                int page_stride, int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink,
-                               float out_scale) {
+                               float out_scale, const float* __restrict__ distance, int sigmoid_weights, const float* __restrict__ head_offset,
+                               const T* __restrict__ gate, long long gate_stride, int gate_per_head) {
     grid_dependents_launch();
     grid_dependency_wait();
     constexpr int kPer = Word<T>::kElements;
@@ -279,6 +301,8 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
         for (int column = lane; column < dim; column += 32)
             query_rows[warp * dim + column] = to_float(queries[(static_cast<size_t>(token) * heads + head) * dim + column]) * scale;
     const float* query = query_rows + warp * dim;
+    const float far = distance ? distance[2 * head] : 0.0f, reach = distance ? distance[2 * head + 1] : 0.0f;
+    const float offset = head_offset ? head_offset[head] : 0.0f;
     float top = sink ? 0.0f : -INFINITY, sum = sink ? 1.0f : 0.0f;
     float acc[kMaxOwned];
 #pragma unroll
@@ -300,14 +324,20 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
                     if (kPer == 2) b = fmaf(query[word * kPer + 1], Word<T>::second(both), b);
                 }
                 score = a + b;
+                if (distance) score -= far * log1pf(reach * static_cast<float>(position - (base + lane)));
             }
-            const float new_top = fmaxf(top, warp_max(score));
-            const float p = lane < count ? expf(score - new_top) : 0.0f;
-            const float keep = expf(top - new_top);
-            sum = sum * keep + warp_sum(p);
-            top = new_top;
+            float p;
+            if (sigmoid_weights) {
+                p = lane < count ? 1.0f / (1.0f + expf(-(score + offset))) : 0.0f;
+            } else {
+                const float new_top = fmaxf(top, warp_max(score));
+                p = lane < count ? expf(score - new_top) : 0.0f;
+                const float keep = expf(top - new_top);
+                sum = sum * keep + warp_sum(p);
+                top = new_top;
 #pragma unroll
-            for (int i = 0; i < kMaxOwned; ++i) acc[i] *= keep;
+                for (int i = 0; i < kMaxOwned; ++i) acc[i] *= keep;
+            }
             const uint32_t* v = buffer + kTileKeys * key_stride;
             for (int j = 0; j < count; ++j) {
                 const float w = __shfl_sync(0xffffffffu, p, j);
@@ -327,14 +357,19 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
     }
     copy_wait<0>();
     if (!has_head) return;
-    const float factor = out_scale / sum;
+    const float factor = sigmoid_weights ? out_scale : out_scale / sum;
     T* target = out + static_cast<size_t>(token) * out_stride + head * vdim;
+    const T* gates = gate ? gate + static_cast<size_t>(token) * gate_stride + (gate_per_head ? head : head * vdim) : nullptr;
 #pragma unroll
     for (int i = 0; i < kMaxOwned / kPer; ++i) {
         const int word = lane + 32 * i;
         if (word < value_words) {
-            target[word * kPer] = from_float<T>(acc[i * kPer] * factor);
-            if (kPer == 2) target[word * kPer + 1] = from_float<T>(acc[i * kPer + 1] * factor);
+#pragma unroll
+            for (int e = 0; e < kPer; ++e) {
+                float value = acc[i * kPer + e] * factor;
+                if (gates) value /= 1.0f + expf(-to_float(gates[gate_per_head ? 0 : word * kPer + e]));
+                target[word * kPer + e] = from_float<T>(value);
+            }
         }
     }
 }
@@ -351,7 +386,8 @@ int staged_bytes(int dim, int vdim) {
 template <typename T>
 int launch_staged(int bytes, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
                   const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
-                  float scale, int window, int chunk, int sink, float out_scale, cudaStream_t s) {
+                  float scale, int window, int chunk, int sink, float out_scale, const float* distance, int sigmoid_weights, const float* head_offset,
+                  const void* gate, long long gate_stride, int gate_per_head, cudaStream_t s) {
     static int allowed = 48 * 1024;
     if (bytes > allowed) {
         cudaError_t status = cudaFuncSetAttribute(masked_attention_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -361,7 +397,8 @@ int launch_staged(int bytes, const void* queries, const void* rows, const void* 
     const int group_size = heads / kv_heads, passes = (group_size + kStagedWarps - 1) / kStagedWarps;
     tau_launch(masked_attention_staged_kernel<T>, dim3(tokens, kv_heads * passes), dim3(kStagedWarps * 32), bytes, s, static_cast<const T*>(queries),
                static_cast<const T*>(rows), static_cast<const T*>(value_pages), static_cast<T*>(out), out_stride, positions, token_seq, page_rows, page_stride,
-               page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale);
+               page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance, sigmoid_weights, head_offset,
+               static_cast<const T*>(gate), gate_stride, gate_per_head);
     return tau_launch_status();
 }
 
@@ -370,7 +407,7 @@ int launch_staged(int bytes, const void* queries, const void* rows, const void* 
 TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
                                   const float* frequency, int rotary, float magnitude, void* queries, void* rows, void* value_pages, const int* positions,
                                   const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
-                                  int write_rows, void* stream) {
+                                  int write_rows, float temperature_coef, int temperature_every, void* stream) {
     if (tokens <= 0) return 0;
     if (!projected || !queries || !positions || heads <= 0 || kv_heads <= 0 || dim <= 0 || vdim <= 0 || rotary < 0 || rotary > dim || rotary % 2 != 0 ||
         (rotary && !frequency) || (write_rows && (!rows || !token_seq || !page_rows)))
@@ -381,7 +418,7 @@ TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long pr
 #define TAU_PREPARE(T)                                                                                                                            \
     tau_launch(masked_prepare_kernel<T>, dim3(tokens), dim3(kWarps * 32), bytes, s, static_cast<const T*>(projected), projected_stride, q_weight, k_weight, eps, \
                frequency, rotary, magnitude, static_cast<T*>(queries), static_cast<T*>(rows), static_cast<T*>(value_pages), positions, token_seq, page_rows, page_stride, page_tokens, heads,   \
-               kv_heads, dim, vdim, write_rows)
+               kv_heads, dim, vdim, write_rows, temperature_coef, temperature_every)
     if (dtype == TAU_F32) TAU_PREPARE(float);
     else if (dtype == TAU_BF16) TAU_PREPARE(bf16);
     else return cudaErrorInvalidValue;
@@ -393,10 +430,11 @@ TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long pr
 // of their own, `rows` [pages, kv_heads, page_tokens, dim] and `value_pages` [pages, kv_heads, page_tokens, vdim].
 TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
                                     const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
-                                    int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, int staged, void* stream) {
+                                    int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, int staged, const float* distance,
+                                    int sigmoid_weights, const float* head_offset, const void* gate, long long gate_stride, int gate_per_head, void* stream) {
     if (tokens <= 0) return 0;
     if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim <= 0 ||
-        vdim <= 0 || vdim > 32 * kMaxOwned || window < 0 || chunk < 0 || (window > 0 && chunk > 0))
+        vdim <= 0 || vdim > 32 * kMaxOwned || window < 0 || chunk < 0 || (window > 0 && chunk > 0) || (sigmoid_weights && sink))
         return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // `staged` (steps of single tokens): the kernel that shares tiles of the cache among a group's heads, where the sizes allow it.
@@ -405,9 +443,11 @@ TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* 
         if (staged_size > 0) {
             if (dtype == TAU_F32)
                 return launch_staged<float>(staged_size, queries, rows, value_pages, out, out_stride, positions, token_seq, page_rows, page_stride, page_tokens,
-                                            tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, s);
+                                            tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance, sigmoid_weights, head_offset, gate, gate_stride,
+                                            gate_per_head, s);
             return launch_staged<bf16>(staged_size, queries, rows, value_pages, out, out_stride, positions, token_seq, page_rows, page_stride, page_tokens,
-                                       tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, s);
+                                       tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance, sigmoid_weights, head_offset, gate, gate_stride,
+                                       gate_per_head, s);
         }
     }
     const size_t bytes = static_cast<size_t>(kWarps) * dim * sizeof(float);
@@ -415,7 +455,8 @@ TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* 
     dim3 grid(tokens, (heads + kWarps - 1) / kWarps);
 #define TAU_ATTEND(T)                                                                                                                         \
     tau_launch(masked_attention_kernel<T>, grid, dim3(kWarps * 32), bytes, s, static_cast<const T*>(queries), static_cast<const T*>(rows), static_cast<const T*>(value_pages), static_cast<T*>(out), \
-               out_stride, positions, token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale)
+               out_stride, positions, token_seq, page_rows, page_stride, page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance,         \
+               sigmoid_weights, head_offset, static_cast<const T*>(gate), gate_stride, gate_per_head)
     if (dtype == TAU_F32) TAU_ATTEND(float);
     else if (dtype == TAU_BF16) TAU_ATTEND(bf16);
     else return cudaErrorInvalidValue;

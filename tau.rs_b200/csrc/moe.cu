@@ -7,6 +7,9 @@
 //   gate_up:  inner[token, place] = silu(W_gate[e] h) * (W_up[e] h) for the expert e of each (token, place).
 //   down:     out[token] = sum over places of weight * (W_down[e] inner[token, place]) + shared_gate * shared[token], 32-bit.
 //
+// Experts numbered `real_experts` and up have no weights: they return what they read (identity experts), so a pair that chose one adds
+// weight * h to the token's sum.
+//
 // These are weight-streaming kernels: a warp per output feature, the activation row in shared memory as floats.
 #include "common.cuh"
 
@@ -190,11 +193,12 @@ moe_route_kernel(const T* __restrict__ hidden, const float* __restrict__ router,
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 moe_gate_up_kernel(const T* __restrict__ hidden, const T* __restrict__ gate_up, const int* __restrict__ chosen, const float* __restrict__ input_weights,
-                   T* __restrict__ inner_out, int width, int inner, int top, int features_per_block, int interleave) {
+                   T* __restrict__ inner_out, int width, int inner, int top, int features_per_block, int interleave, int real_experts) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ __align__(16) float row[];
     const int pair = blockIdx.x, token = pair / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (chosen[pair] >= real_experts) return;      // an identity expert has no inner features
     for (int column = threadIdx.x; column < width; column += blockDim.x) row[column] = to_float(hidden[static_cast<size_t>(token) * width + column]);
     __syncthreads();
     const T* weights = gate_up + static_cast<size_t>(chosen[pair]) * 2 * inner * width;
@@ -218,29 +222,39 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads)
 moe_down_kernel(const T* __restrict__ inner_in, const T* __restrict__ down, const int* __restrict__ chosen, const float* __restrict__ weights,
                 const T* __restrict__ shared_out, const float* __restrict__ shared_gate, float* __restrict__ out, int width, int inner, int top,
-                int features_per_block) {
+                int features_per_block, const T* __restrict__ hidden, int real_experts) {
     grid_dependents_launch();
     grid_dependency_wait();
     extern __shared__ __align__(16) float rows[];     // [top][inner]
     const int token = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int item = threadIdx.x; item < top * inner; item += blockDim.x) rows[item] = to_float(inner_in[static_cast<size_t>(token) * top * inner + item]);
+    for (int item = threadIdx.x; item < top * inner; item += blockDim.x)      // an identity expert's place was never written: nothing of it is read
+        rows[item] = chosen[static_cast<size_t>(token) * top + item / inner] < real_experts ? to_float(inner_in[static_cast<size_t>(token) * top * inner + item]) : 0.0f;
     __syncthreads();
     const int begin = blockIdx.y * features_per_block, end = min(width, begin + features_per_block);
     for (int feature = begin + warp; feature < end; feature += kWarps) {
         float sum = 0.0f;
         int place = 0;
+        // What one place adds: its expert's row against the place's inner features, or the token's own feature for an identity expert.
+        auto alone = [&](int at) {
+            const int expert = chosen[static_cast<size_t>(token) * top + at];
+            if (expert >= real_experts) return hidden ? to_float(hidden[static_cast<size_t>(token) * width + feature]) : 0.0f;
+            return warp_dot(down + (static_cast<size_t>(expert) * width + feature) * inner, rows + at * inner, inner, lane);
+        };
         for (; place + 1 < top; place += 2) {     // two places at a time, summed in place order
-            const T* first = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place]) * width + feature) * inner;
-            const T* second = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place + 1]) * width + feature) * inner;
+            const int e0 = chosen[static_cast<size_t>(token) * top + place], e1 = chosen[static_cast<size_t>(token) * top + place + 1];
             float a, b;
-            warp_dot_pair(first, rows + place * inner, second, rows + (place + 1) * inner, inner, lane, a, b);
+            if (e0 < real_experts && e1 < real_experts) {
+                const T* first = down + (static_cast<size_t>(e0) * width + feature) * inner;
+                const T* second = down + (static_cast<size_t>(e1) * width + feature) * inner;
+                warp_dot_pair(first, rows + place * inner, second, rows + (place + 1) * inner, inner, lane, a, b);
+            } else {
+                a = alone(place);
+                b = alone(place + 1);
+            }
             sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, a, sum);
             sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place + 1] : 1.0f, b, sum);
         }
-        if (place < top) {
-            const T* weight_row = down + (static_cast<size_t>(chosen[static_cast<size_t>(token) * top + place]) * width + feature) * inner;
-            sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, warp_dot(weight_row, rows + place * inner, inner, lane), sum);
-        }
+        if (place < top) sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, alone(place), sum);
         if (lane == 0) {
             if (shared_out) sum += (shared_gate ? shared_gate[token] : 1.0f) * to_float(shared_out[static_cast<size_t>(token) * width + feature]);
             out[static_cast<size_t>(token) * width + feature] = sum;
@@ -297,14 +311,19 @@ __global__ void moe_gather_kernel(const T* __restrict__ hidden, const int* __res
 // out[token] = sum over places of weight * rows[position[token, place]] + shared_gate * shared[token], in place order.
 template <typename T>
 __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __restrict__ position, const float* __restrict__ weights,
-                                   const T* __restrict__ shared_out, const float* __restrict__ shared_gate, float* __restrict__ out, int width, int top) {
+                                   const T* __restrict__ shared_out, const float* __restrict__ shared_gate, float* __restrict__ out, int width, int top,
+                                   const int* __restrict__ chosen, const T* __restrict__ hidden, int real_experts) {
     grid_dependents_launch();
     grid_dependency_wait();
     const int token = blockIdx.x;
     for (int column = threadIdx.x; column < width; column += blockDim.x) {
         float sum = 0.0f;
-        for (int place = 0; place < top; ++place)
-            sum = fmaf(weights ? weights[static_cast<size_t>(token) * top + place] : 1.0f, rows[static_cast<size_t>(position[static_cast<size_t>(token) * top + place]) * width + column], sum);
+        for (int place = 0; place < top; ++place) {
+            const size_t pair = static_cast<size_t>(token) * top + place;
+            const bool identity = chosen && chosen[pair] >= real_experts;      // such a pair's row was never computed
+            const float row = identity ? to_float(hidden[static_cast<size_t>(token) * width + column]) : rows[static_cast<size_t>(position[pair]) * width + column];
+            sum = fmaf(weights ? weights[pair] : 1.0f, row, sum);
+        }
         if (shared_out) sum += (shared_gate ? shared_gate[token] : 1.0f) * to_float(shared_out[static_cast<size_t>(token) * width + column]);
         out[static_cast<size_t>(token) * width + column] = sum;
     }
@@ -312,7 +331,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ rows, const int* __
 
 template <typename T>
 int launch_all(int what, const void* a, const void* b, const void* c, const void* d, const void* e, const void* f, void* o1, void* o2, void* o3,
-               int tokens, int width, int inner, int experts, int top, int flag_a, int flag_b, cudaStream_t s) {
+               int tokens, int width, int inner, int experts, int top, int flag_a, int flag_b, cudaStream_t s, const void* g = nullptr) {
     if (what == 0) {
         const size_t bytes = (static_cast<size_t>(width) + 2 * experts) * sizeof(float);
         if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_route_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
@@ -325,7 +344,7 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
         if (bytes > 48 * 1024 && cudaFuncSetAttribute(moe_gate_up_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess)
             return cudaErrorInvalidValue;
         tau_launch(moe_gate_up_kernel<T>, dim3(tokens * top, (inner + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a),
-                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<const float*>(d), static_cast<T*>(o1), width, inner, top, per_block, flag_a);
+                   static_cast<const T*>(b), static_cast<const int*>(c), static_cast<const float*>(d), static_cast<T*>(o1), width, inner, top, per_block, flag_a, experts);
     } else {
         const int per_block = tokens * ((width + 63) / 64) >= 1024 ? 64 : tokens * ((width + 31) / 32) >= 1024 ? 32 : 16;   // few tokens: smaller tiles, more blocks
         const size_t bytes = static_cast<size_t>(top) * inner * sizeof(float);
@@ -333,7 +352,7 @@ int launch_all(int what, const void* a, const void* b, const void* c, const void
             return cudaErrorInvalidValue;
         tau_launch(moe_down_kernel<T>, dim3(tokens, (width + per_block - 1) / per_block), dim3(kThreads), bytes, s, static_cast<const T*>(a), static_cast<const T*>(b),
                    static_cast<const int*>(c), static_cast<const float*>(d), static_cast<const T*>(e), static_cast<const float*>(f), static_cast<float*>(o1),
-                   width, inner, top, per_block);
+                   width, inner, top, per_block, static_cast<const T*>(g), experts);
     }
     return tau_launch_status();
 }
@@ -351,23 +370,25 @@ TAU_EXPORT int tau_moe_route(int dtype, const void* hidden, const float* router,
     return cudaErrorInvalidValue;
 }
 
+// `real_experts`: experts with weights (gate_up holds that many); a pair that chose a higher number is left alone.
 TAU_EXPORT int tau_moe_gate_up(int dtype, const void* hidden, const void* gate_up, const int* chosen, const float* input_weights, void* inner_out, int tokens,
-                               int width, int inner, int top, int interleave, void* stream) {
+                               int width, int inner, int top, int interleave, int real_experts, void* stream) {
     if (tokens <= 0) return 0;
     if (!hidden || !gate_up || !chosen || !inner_out || width <= 0 || inner <= 0 || top <= 0 || static_cast<long long>(tokens) * top > 0x7fffffff) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, input_weights, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
-    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, input_weights, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, 0, top, interleave, 0, s);
+    if (dtype == TAU_F32) return launch_all<float>(1, hidden, gate_up, chosen, input_weights, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, real_experts, top, interleave, 0, s);
+    if (dtype == TAU_BF16) return launch_all<bf16>(1, hidden, gate_up, chosen, input_weights, nullptr, nullptr, inner_out, nullptr, nullptr, tokens, width, inner, real_experts, top, interleave, 0, s);
     return cudaErrorInvalidValue;
 }
 
 TAU_EXPORT int tau_moe_down(int dtype, const void* inner_in, const void* down, const int* chosen, const float* weights, const void* shared_out,
-                            const float* shared_gate, float* out, int tokens, int width, int inner, int top, void* stream) {
+                            const float* shared_gate, float* out, int tokens, int width, int inner, int top, const void* hidden, int real_experts,
+                            void* stream) {
     if (tokens <= 0) return 0;
     if (!inner_in || !down || !chosen || !out || width <= 0 || inner <= 0 || top <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) return launch_all<float>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
-    if (dtype == TAU_BF16) return launch_all<bf16>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, 0, top, 0, 0, s);
+    if (dtype == TAU_F32) return launch_all<float>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, real_experts, top, 0, 0, s, hidden);
+    if (dtype == TAU_BF16) return launch_all<bf16>(2, inner_in, down, chosen, weights, shared_out, shared_gate, out, nullptr, nullptr, tokens, width, inner, real_experts, top, 0, 0, s, hidden);
     return cudaErrorInvalidValue;
 }
 
@@ -391,12 +412,12 @@ TAU_EXPORT int tau_moe_gather(int dtype, const void* hidden, const int* order, c
 }
 
 TAU_EXPORT int tau_moe_combine(int dtype, const float* rows, const int* position, const float* weights, const void* shared_out, const float* shared_gate,
-                               float* out, int tokens, int width, int top, void* stream) {
+                               float* out, int tokens, int width, int top, const int* chosen, const void* hidden, int real_experts, void* stream) {
     if (tokens <= 0) return 0;
-    if (!rows || !position || !out || width <= 0 || top <= 0) return cudaErrorInvalidValue;
+    if (!rows || !position || !out || width <= 0 || top <= 0 || (chosen && !hidden)) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == TAU_F32) tau_launch(moe_combine_kernel<float>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const float*>(shared_out), shared_gate, out, width, top);
-    else if (dtype == TAU_BF16) tau_launch(moe_combine_kernel<bf16>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const bf16*>(shared_out), shared_gate, out, width, top);
+    if (dtype == TAU_F32) tau_launch(moe_combine_kernel<float>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const float*>(shared_out), shared_gate, out, width, top, chosen, static_cast<const float*>(hidden), real_experts);
+    else if (dtype == TAU_BF16) tau_launch(moe_combine_kernel<bf16>, dim3(tokens), dim3(kThreads), 0, s, rows, position, weights, static_cast<const bf16*>(shared_out), shared_gate, out, width, top, chosen, static_cast<const bf16*>(hidden), real_experts);
     else return cudaErrorInvalidValue;
     return tau_launch_status();
 }

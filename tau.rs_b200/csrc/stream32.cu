@@ -23,39 +23,85 @@ __global__ void embedding_f32_kernel(const int* __restrict__ tokens, const T* __
     for (int column = threadIdx.x; column < width; column += blockDim.x) target[column] = inside ? to_float(source[column]) * scale : 0.0f;
 }
 
-// r = rows ? rows[i] : i.  sum = stream[r] + (a[r] + b[r]) in 32-bit; if `update` the sum replaces stream[r];
-// out[i] = sum / sqrt(mean(sum^2) + eps) * weight, rounded once to T.
+// r = rows ? rows[i] : i.  sum = stream[r] + branch_scale * (a[r] + b[r]) in 32-bit; if `update` the sum replaces stream[r];
+// out[i] = sum / sqrt(mean(sum^2) + eps) * weight, rounded once to T.  With `groups` > 1 the row is cut into that many equal
+// consecutive pieces and each is divided by its own root mean square (a warp sums a piece's squares).
+constexpr int kMaxNormGroups = 64;
+
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 stream_add_norm_kernel(float* __restrict__ stream, const void* __restrict__ a, int a_code, const void* __restrict__ b, int b_code,
-                       const int* __restrict__ rows, const float* __restrict__ weight, T* __restrict__ out, int width, float eps, int update) {
+                       const int* __restrict__ rows, const float* __restrict__ weight, T* __restrict__ out, int width, float eps, int update,
+                       int groups, float branch_scale) {
     grid_dependents_launch();
     grid_dependency_wait();
     __shared__ float scratch[33];
+    __shared__ float inverses[kMaxNormGroups];
     const int row = rows ? rows[blockIdx.x] : blockIdx.x;
     const size_t base = static_cast<size_t>(row) * width;
-    float squares = 0.0f;
-    for (int column = threadIdx.x; column < width; column += blockDim.x) {
+    auto joined = [&](int column) {
         float value = stream[base + column];
         if (a) {
             float branch = load_as_float(a, a_code, base + column);
             if (b) branch += load_as_float(b, b_code, base + column);
-            value += branch;
+            value = fmaf(branch_scale, branch, value);
         }
+        return value;
+    };
+    T* target = out + static_cast<size_t>(blockIdx.x) * width;
+    if (groups > 1) {
+        if (update && a) {
+            for (int column = threadIdx.x; column < width; column += blockDim.x) stream[base + column] = joined(column);
+            __syncthreads();      // the pieces below are summed by other threads than those that wrote them
+        }
+        const bool stored = update || !a;
+        const int piece = width / groups, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+        for (int group = warp; group < groups; group += warps) {
+            float squares = 0.0f;
+            for (int column = group * piece + lane; column < (group + 1) * piece; column += 32) {
+                const float value = stored ? stream[base + column] : joined(column);
+                squares = fmaf(value, value, squares);
+            }
+            squares = warp_sum(squares);
+            if (lane == 0) inverses[group] = 1.0f / sqrtf(squares / static_cast<float>(piece) + eps);
+        }
+        __syncthreads();
+        for (int column = threadIdx.x; column < width; column += blockDim.x)
+            target[column] = from_float<T>((stored ? stream[base + column] : joined(column)) * inverses[column / piece] * weight[column]);
+        return;
+    }
+    float squares = 0.0f;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) {
+        const float value = joined(column);
         if (update) stream[base + column] = value;
         squares += value * value;
     }
     const float inverse = 1.0f / sqrtf(block_sum(squares, scratch) / static_cast<float>(width) + eps);
-    T* target = out + static_cast<size_t>(blockIdx.x) * width;
     for (int column = threadIdx.x; column < width; column += blockDim.x) {
-        float value = stream[base + column];     // each thread reads back what it wrote itself
-        if (a && !update) {
-            float branch = load_as_float(a, a_code, base + column);
-            if (b) branch += load_as_float(b, b_code, base + column);
-            value += branch;
-        }
+        const float value = (a && !update) ? joined(column) : stream[base + column];     // each thread reads back what it wrote itself
         target[column] = from_float<T>(value * inverse * weight[column]);
     }
+}
+
+// out[row] = left_scale * left[row] / rms(left[row]) * left_weight + right_scale * right[row] / rms(right[row]) * right_weight: two results
+// that are normalised over their whole width, each with its own weight, before they are added (eps inside the roots); all 32-bit.
+__global__ void __launch_bounds__(kThreads)
+normed_pair_sum_kernel(const float* __restrict__ left, const float* __restrict__ right, const float* __restrict__ left_weight,
+                       const float* __restrict__ right_weight, float* __restrict__ out, int width, float eps, float left_scale, float right_scale) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    __shared__ float scratch[33];
+    const size_t base = static_cast<size_t>(blockIdx.x) * width;
+    float a = 0.0f, b = 0.0f;
+    for (int column = threadIdx.x; column < width; column += blockDim.x) {
+        const float x = left[base + column], y = right[base + column];
+        a = fmaf(x, x, a);
+        b = fmaf(y, y, b);
+    }
+    const float left_factor = left_scale / sqrtf(block_sum(a, scratch) / static_cast<float>(width) + eps);
+    const float right_factor = right_scale / sqrtf(block_sum(b, scratch) / static_cast<float>(width) + eps);
+    for (int column = threadIdx.x; column < width; column += blockDim.x)
+        out[base + column] = left[base + column] * left_factor * left_weight[column] + right[base + column] * right_factor * right_weight[column];
 }
 
 // values [rows, groups * group_width] in 32-bit.  With `normalize` each group of a row is divided by its root mean square;
@@ -131,13 +177,24 @@ TAU_EXPORT int tau_embedding_f32(int table_dtype, const int* tokens, const void*
 }
 
 TAU_EXPORT int tau_stream_add_norm(int out_dtype, float* stream_values, const void* a, int a_dtype, const void* b, int b_dtype, const int* rows,
-                                   const float* weight, void* out, int out_rows, int width, float eps, int update, void* stream) {
+                                   const float* weight, void* out, int out_rows, int width, float eps, int update, int groups, float branch_scale,
+                                   void* stream) {
     if (out_rows <= 0) return 0;
-    if (!stream_values || !weight || !out || width <= 0 || (b && !a) || (update && rows)) return cudaErrorInvalidValue;
+    if (!stream_values || !weight || !out || width <= 0 || (b && !a) || (update && rows) || groups < 1 || groups > kMaxNormGroups || width % groups != 0)
+        return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (out_dtype == TAU_F32) tau_launch(stream_add_norm_kernel<float>, dim3(out_rows), dim3(kThreads), 0, s, stream_values, a, a_dtype, b, b_dtype, rows, weight, static_cast<float*>(out), width, eps, update);
-    else if (out_dtype == TAU_BF16) tau_launch(stream_add_norm_kernel<bf16>, dim3(out_rows), dim3(kThreads), 0, s, stream_values, a, a_dtype, b, b_dtype, rows, weight, static_cast<bf16*>(out), width, eps, update);
+    if (out_dtype == TAU_F32) tau_launch(stream_add_norm_kernel<float>, dim3(out_rows), dim3(kThreads), 0, s, stream_values, a, a_dtype, b, b_dtype, rows, weight, static_cast<float*>(out), width, eps, update, groups, branch_scale);
+    else if (out_dtype == TAU_BF16) tau_launch(stream_add_norm_kernel<bf16>, dim3(out_rows), dim3(kThreads), 0, s, stream_values, a, a_dtype, b, b_dtype, rows, weight, static_cast<bf16*>(out), width, eps, update, groups, branch_scale);
     else return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
+
+TAU_EXPORT int tau_normed_pair_sum(const float* left, const float* right, const float* left_weight, const float* right_weight, float* out, int rows, int width,
+                                   float eps, float left_scale, float right_scale, void* stream) {
+    if (rows <= 0) return 0;
+    if (!left || !right || !left_weight || !right_weight || !out || width <= 0) return cudaErrorInvalidValue;
+    tau_launch(normed_pair_sum_kernel, dim3(rows), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), left, right, left_weight, right_weight, out, width, eps,
+               left_scale, right_scale);
     return tau_launch_status();
 }
 

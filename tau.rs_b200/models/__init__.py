@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers each of them by name."""
-from . import bisudra, fasesun, pegurax, qwen3  # noqa: F401
+from . import bisudra, fasesun, nugolorn, pegurax, qwen3  # noqa: F401

@@ -39,6 +39,18 @@ class CacheNeed:
     chunk: Optional[int] = None
 
 
+class Pending(tuple):
+    """Results that have yet to join the residual stream (one or two tensors), and the factor that they join it with: the norm that
+    adds them computes `stream + scale * (sum of the results)`."""
+
+    scale = 1.0
+
+    def __new__(cls, results, scale: float = 1.0):
+        pending = super().__new__(cls, results)
+        pending.scale = float(scale)
+        return pending
+
+
 class Part:
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}

@@ -79,7 +79,9 @@ class ParallelBlock(Block):
 
     The residual stream `x` is 32-bit whatever the activations' dtype.  The block hands on `(x, (mixer's output,
     feed-forward's output))`; the next block's norm (or the model's last one) adds the two in 32-bit, adds that to the
-    stream and normalises, in one kernel.  Weight names: `<prefix>.norm1`, `<prefix>.mix.*`, `<prefix>.mlp.*`.
+    stream and normalises, in one kernel.  With `residual_scale` m the sum joins as `x + m * (mixer(h) + feed_forward(h))`.
+    What the mixer keeps beside its cache (`extra_cache_needs`) is the block's as well.  Weight names: `<prefix>.norm1`,
+    `<prefix>.mix.*`, `<prefix>.mlp.*`.
     """
 
     mixer_name = "mix"
@@ -104,12 +106,18 @@ class ParallelBlock(Block):
     finalize_weights = PreNormBlock.finalize_weights
     bytes_read_per_step = PreNormBlock.bytes_read_per_step
 
+    def extra_cache_needs(self):
+        return self.mixer.extra_cache_needs()
+
     def forward(self, residual, branch, step, cache, writes_cache: bool):
+        from .base import Pending
+
         normalized = self.norm.forward(residual) if branch is None else self.norm.add_forward(branch, residual)
         mixed = self.mixer.forward(normalized, step, cache, writes_cache)
+        scale = getattr(self.spec, "residual_scale", 1.0)
         if self.feed_forward is None:
-            return residual, mixed
-        return residual, (mixed, self.feed_forward.forward(normalized, step))
+            return residual, (mixed if scale == 1.0 else Pending((mixed,), scale))
+        return residual, Pending((mixed, self.feed_forward.forward(normalized, step)), scale)
 
 
 @register_block("sublayer_norm")

@@ -24,8 +24,9 @@ class StackedLinear(Part):
     """
 
     def __init__(self, pieces: Sequence[Tuple[str, int]], in_features: int, bias: bool, dtype, device, interleave: int = 0,
-                 weight_suffix: str = ".weight", bias_suffix: str = ".bias"):
-        """The tensors are named `<prefix><weight_suffix>` and `<prefix><bias_suffix>`.  `interleave` > 0 (two pieces of equal size, no bias): rows are stored in groups of `interleave` rows of the
+                 weight_suffix: str = ".weight", bias_suffix: str = ".bias", biased: Optional[Sequence[str]] = None):
+        """`biased` (with `bias`): only the pieces whose prefixes it lists have a bias tensor; the others' part of the stacked bias is zero.
+        The tensors are named `<prefix><weight_suffix>` and `<prefix><bias_suffix>`.  `interleave` > 0 (two pieces of equal size, no bias): rows are stored in groups of `interleave` rows of the
         first piece followed by the matching rows of the second, which is what a gated product reads."""
         self.interleave = interleave
         self.weight_suffix, self.bias_suffix = weight_suffix, bias_suffix
@@ -33,6 +34,7 @@ class StackedLinear(Part):
         self.in_features = in_features
         self.out_features = sum(width for _, width in self.pieces)
         self.has_bias = bias
+        self.biased = None if biased is None else set(biased)
         self.dtype, self.device = dtype, device
         self._parts = {}
         self.weight: Optional[torch.Tensor] = None
@@ -42,7 +44,7 @@ class StackedLinear(Part):
         specs = {}
         for prefix, width in self.pieces:
             specs[f"{prefix}{self.weight_suffix}"] = TensorSpec((width, self.in_features), role="matrix")
-            if self.has_bias:
+            if self.has_bias and (self.biased is None or prefix in self.biased):
                 specs[f"{prefix}{self.bias_suffix}"] = TensorSpec((width,), role="vector")
         return specs
 
@@ -61,7 +63,9 @@ class StackedLinear(Part):
             self.weight = weights[0] if len(weights) == 1 else torch.cat(weights, dim=0).contiguous()
         del weights
         if self.has_bias:
-            biases = [self._parts.pop(f"{prefix}{self.bias_suffix}") for prefix, _ in self.pieces]
+            like = next(tensor for name, tensor in self._parts.items() if name.endswith(self.bias_suffix))
+            biases = [self._parts.pop(f"{prefix}{self.bias_suffix}") if self.biased is None or prefix in self.biased else torch.zeros(width, dtype=like.dtype, device=like.device)
+                      for prefix, width in self.pieces]
             self.bias = biases[0] if len(biases) == 1 else torch.cat(biases, dim=0).contiguous()
 
     def forward_gated(self, values):

@@ -119,6 +119,12 @@ class DecoderModel:
             part.finalize_weights()
         if self.spec.tie_head:
             self.head = self.embedding
+        scale = getattr(self.spec, "logit_scale", 1.0)
+        if scale != 1.0:      # the head is linear: the last norm's weight (and bias) carry the logits' factor
+            norm = self.final_norm
+            norm.weight = (norm.weight * scale).contiguous()
+            if getattr(norm, "bias", None) is not None:
+                norm.bias = (norm.bias * scale).contiguous()
 
     def weight_bytes(self) -> int:
         """Bytes of weights that one step reads: what each part says it reads (every tensor once, unless a part knows

@@ -1,4 +1,5 @@
-"""RMSNorm: `x * rsqrt(mean(x^2) + eps) * w`, statistic in 32-bit, one rounding.
+"""RMSNorm: `x * rsqrt(mean(x^2) + eps) * w`, statistic in 32-bit, one rounding; with `groups` > 1 each of that many equal
+consecutive pieces of the row is divided by its own root mean square.
 
 crates/models/src/components/rms_norm.rs:205-210 and :147-150; the in-tree norm scales
 by `1 + w`, this part by `w`.  The fused form first rounds `residual + branch` to the
@@ -33,12 +34,12 @@ class RMSNorm(Norm):
     def forward(self, values, rows=None, branch=None):
         count = values.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((count, self.spec.width), dtype=self.dtype or values.dtype, device=values.device)
-        kernels.rms_norm(values, self.weight, self.spec.eps, out, rows, branch)
+        kernels.rms_norm(values, self.weight, self.spec.eps, out, rows, branch, getattr(self.spec, "groups", 1), getattr(branch, "scale", 1.0))
         return out
 
     def add_forward(self, branch, residual):
         out = torch.empty(residual.shape, dtype=self.dtype or residual.dtype, device=residual.device)
-        kernels.add_rms_norm(branch, residual, self.weight, self.spec.eps, out)
+        kernels.add_rms_norm(branch, residual, self.weight, self.spec.eps, out, getattr(self.spec, "groups", 1), getattr(branch, "scale", 1.0))
         return out
 
 

@@ -15,6 +15,9 @@ The router, the choice and the weighted sum are 32-bit, and so is the output.  T
   product), and a last kernel sums each token's places in place order.  The host reads the experts' row counts for this
   (one small copy per layer), which a prompt's step can afford and a captured decode step could not.
 
+`identity` experts have no tensors: the router scores them like the others (its last outputs), and a token that chooses one adds
+its weight times the token itself.  The expert kernels skip such places and the summing kernels put the token's row in their stead.
+
 Both compute the same sums in 32-bit from the same roundings of the inputs; they differ as two product kernels differ.
 A step reads only the experts that its tokens chose, which `bytes_read_per_step` accounts for.  Tensor names under the
 prefix: `router`, `router.b`, `correction`, `e<j>.gate`, `e<j>.up`, `e<j>.down`, `shared.gate|up|down`, `shared.sg`.
@@ -37,19 +40,25 @@ class RoutedExperts(FeedForward):
     def __init__(self, spec, prefix: str, dtype, device):
         if spec.score not in ("sigmoid", "softmax"):
             raise ValueError(f"unknown router score {spec.score!r}")
-        if not 1 <= spec.top <= spec.experts:
-            raise ValueError("top must lie between 1 and the number of experts")
+        if spec.top < 1 or spec.experts < 1:
+            raise ValueError("top and the number of experts must be positive")
         if getattr(spec, "weigh", "output") not in ("output", "input"):
             raise ValueError(f"the experts' weights act on their output or their input, not on {spec.weigh!r}")
         if spec.shared_gate and spec.shared is None:
             raise ValueError("a shared gate needs a shared expert")
         self.spec, self.prefix, self.dtype = spec, prefix, dtype
+        self.identity = getattr(spec, "identity", 0)
+        if self.identity < 0:
+            raise ValueError("the number of identity experts cannot be negative")
+        self.outputs = spec.experts + self.identity      # what the router scores
+        if spec.top > self.outputs:
+            raise ValueError("top must lie between 1 and the number of router outputs")
         self.shared = None if spec.shared is None else build("feed_forward", spec.shared, prefix=f"{prefix}.shared", dtype=dtype, device=device)
-        self._own = {f"{prefix}.router": TensorSpec((spec.experts, spec.hidden), role="vector")}
+        self._own = {f"{prefix}.router": TensorSpec((self.outputs, spec.hidden), role="vector")}
         if spec.correction:
-            self._own[f"{prefix}.correction"] = TensorSpec((spec.experts,), role="vector")
+            self._own[f"{prefix}.correction"] = TensorSpec((self.outputs,), role="vector")
         if getattr(spec, "router_bias", False):
-            self._own[f"{prefix}.router.b"] = TensorSpec((spec.experts,), role="vector")
+            self._own[f"{prefix}.router.b"] = TensorSpec((self.outputs,), role="vector")
         if spec.shared_gate:
             self._own[f"{prefix}.shared.sg"] = TensorSpec((1, spec.hidden), role="vector")
         for expert in range(spec.experts):
@@ -98,7 +107,7 @@ class RoutedExperts(FeedForward):
         at most all of them)."""
         spec = self.spec
         element = torch.empty((), dtype=dtype).element_size()
-        total = spec.experts * spec.hidden * 4 + spec.top * 3 * spec.intermediate * spec.hidden * element
+        total = self.outputs * spec.hidden * 4 + min(spec.top, spec.experts) * 3 * spec.intermediate * spec.hidden * element
         return total + (self.shared.bytes_read_per_step(dtype) if self.shared is not None else 0)
 
     def forward(self, hidden, step):
@@ -117,17 +126,17 @@ class RoutedExperts(FeedForward):
         inner = torch.empty((tokens, spec.top, spec.intermediate), dtype=hidden.dtype, device=device)
         on_input = getattr(spec, "weigh", "output") == "input"
         kernels.moe_gate_up(hidden, self.gate_up, chosen, inner, self.interleave, weights if on_input else None)
-        kernels.moe_down(inner, self.down, chosen, None if on_input else weights, shared_out, shared_gate, out)
+        kernels.moe_down(inner, self.down, chosen, None if on_input else weights, shared_out, shared_gate, out, hidden if self.identity else None)
         return out
 
     def _grouped(self, hidden, chosen, weights, shared_out, shared_gate, out) -> None:
         spec = self.spec
         pairs, device = chosen.numel(), hidden.device
-        offsets = torch.empty(spec.experts + 1, dtype=torch.int32, device=device)
+        offsets = torch.empty(self.outputs + 1, dtype=torch.int32, device=device)
         order = torch.empty(pairs, dtype=torch.int32, device=device)
         position = torch.empty(pairs, dtype=torch.int32, device=device)
-        kernels.moe_sort(chosen, spec.experts, offsets, order, position)
-        bounds = offsets.tolist()                        # the host waits here for the router
+        kernels.moe_sort(chosen, self.outputs, offsets, order, position)
+        bounds = offsets.tolist()[: spec.experts + 1]    # the host waits here for the router; identity experts' pairs lie behind and have no product
         gathered = torch.empty((pairs, spec.hidden), dtype=hidden.dtype, device=device)
         on_input = getattr(spec, "weigh", "output") == "input"
         kernels.moe_gather(hidden, order, spec.top, gathered, weights if on_input else None)
@@ -135,4 +144,7 @@ class RoutedExperts(FeedForward):
         rows = torch.empty((pairs, spec.hidden), dtype=torch.float32, device=device)
         kernels.gemm_tc_groups(gathered, self.gate_up, inner, bounds, gated=True)
         kernels.gemm_tc_groups(inner, self.down, rows, bounds)
-        kernels.moe_combine(rows, position, None if on_input else weights, shared_out, shared_gate, out)
+        if self.identity:
+            kernels.moe_combine(rows, position, None if on_input else weights, shared_out, shared_gate, out, chosen, hidden, spec.experts)
+        else:
+            kernels.moe_combine(rows, position, None if on_input else weights, shared_out, shared_gate, out)
