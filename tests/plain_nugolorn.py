@@ -91,7 +91,8 @@ def conv_attention_mixer(h, weights, prefix, mixer, kept=None):
     heads, kv_heads, dim, vdim = mixer["heads"], mixer["kv_heads"], mixer["dim"], mixer["vdim"]
 
     def projected(name):
-        return causal_convolution(h @ weights[f"{prefix}.{name}"].T + weights[f"{prefix}.{name}.b"], weights[f"{prefix}.{name}.conv"])
+        result = h @ weights[f"{prefix}.{name}"].T + weights[f"{prefix}.{name}.b"]
+        return causal_convolution(result, weights[f"{prefix}.{name}.conv"]) if mixer.get("conv") else result
 
     q = projected("q").reshape(tokens, heads, dim)
     if "rot" in mixer and mixer["rot"] is not None:

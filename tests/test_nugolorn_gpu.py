@@ -1,0 +1,561 @@
+"""Nugolorn on the GPU against the plain statement in `plain_nugolorn.py`: each mechanism's kernels alone, then whole models: whole
+prompts, single tokens, portions, unequal batches, slots, pages and states that are used again, keys far back and at page borders,
+long decoding, odd sizes, greedy generation through `generate()`, the command line and the trace replay."""
+import json
+import os
+import subprocess
+import sys
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import nugolorn_models as nm
+import plain_nugolorn as plain
+from helpers import relative_error, run_batched, run_tail_stepwise, run_whole
+from tau_rs_b200 import Engine, StepEntry, generate, load_model
+from tau_rs_b200.csrc import kernels
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+TOLERANCE = {"float32": 5e-5, "bfloat16": 4e-2}
+TORCH = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+DEVICE = "cuda"
+F = torch.float64
+
+
+def close(found, wanted, dtype) -> bool:
+    """float32: every logit within 5e-5 of the largest.  bfloat16 (the plain statement rounds nothing): half of the positions within
+    2e-2 of the largest logit and all but one in ten (or two) within 6e-2; where two experts were a close call the library and the
+    plain statement may choose differently at a position, which says nothing about either (the float32 runs pin every choice)."""
+    if dtype == "float32":
+        return relative_error(found, wanted) < TOLERANCE[dtype]
+    rows = (found.double() - wanted.double()).abs().amax(dim=-1) / wanted.double().abs().max()
+    return float(rows.median()) < 2e-2 and int((rows >= 6e-2).sum()) <= max(2, rows.numel() // 10)
+
+
+def tokens_for(cfg, count, seed):
+    return np.random.default_rng(seed).integers(0, cfg["vocab"], size=count).tolist()
+
+
+_PLAIN = {}
+
+
+def plain_logits(cfg, values, tokens):
+    key = (id(values), tuple(tokens))
+    if key not in _PLAIN:
+        _PLAIN[key] = plain.forward(tokens, {name: value.double() for name, value in values.items()}, cfg).float()
+    return _PLAIN[key]
+
+
+@pytest.fixture(scope="module")
+def models(tmp_path_factory):
+    root = tmp_path_factory.mktemp("nugolorn")
+    made = {}
+    listed = [("mixed", nm.MIXED, 11, {}), ("odd", nm.ODD, 12, {}), ("many_groups", nm.MANY_GROUPS, 13, {}), ("peaky", nm.PEAKY, 14, {"quiet_delta": True}),
+              ("heady", nm.HEADY, 17, {"quiet_delta": True}), ("long_memory", nm.LONG_MEMORY, 16, {"slow_decay": True})]
+    listed += [("only_" + name, cfg, 20 + index, {}) for index, (name, cfg) in enumerate(nm.ONLY.items())]
+    for name, cfg, seed, options in listed:
+        folder = str(root / name)
+        made[name] = (folder, cfg, nm.write_model(folder, cfg, seed, ranks_in_config=name != "mixed", **options))     # one folder whose tensors alone give the ranks
+    return made
+
+
+def engine_of(models, name, dtype, max_tokens=1024):
+    folder, cfg, values = models[name]
+    return Engine(load_model(folder, dtype, "gpu"), max_tokens), cfg, values
+
+
+def on_device(tensor, dtype=torch.float32):
+    return tensor.to(DEVICE, dtype).contiguous()
+
+
+def as_ints(values):
+    return torch.tensor(np.asarray(values, dtype=np.int32), device=DEVICE)
+
+
+def packed_step(runs, slots):
+    """The metadata of a step in which sequence i brings `runs[i]` tokens and sits in cache slot `slots[i]`."""
+    bounds = np.concatenate([[0], np.cumsum(runs)]).astype(np.int32)
+    token_seq = np.concatenate([np.full(count, index, dtype=np.int32) for index, count in enumerate(runs)])
+    return SimpleNamespace(n_seqs=len(runs), token_seq=as_ints(token_seq), cu_seqlens=as_ints(bounds), seq_slot=as_ints(slots),
+                           all_single=all(count == 1 for count in runs))
+
+
+def rand(generator, *shape):
+    return torch.randn(*shape, dtype=F, generator=generator)
+
+
+# ---- the norm in groups, the scaled sum, the two normalised results ------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width, groups", [(96, 3), (100, 1), (100, 50), (192, 4), (64, 64), (1024, 8), (330, 5)])
+def test_the_norm_in_groups_on_the_scaled_sum(dtype, width, groups):
+    generator = torch.Generator().manual_seed(width + groups)
+    stream, a, b, weight = rand(generator, 9, width), rand(generator, 9, width), rand(generator, 9, width), rand(generator, width)
+    kind = TORCH[dtype]
+    a_dev, b_dev = on_device(a, kind), on_device(b)              # a branch in the run's dtype beside one in 32-bit
+    summed = stream.float().double() + 0.7 * (a_dev.double().cpu() + b_dev.double().cpu())
+    wanted = plain.grouped_rms_norm(summed, weight.float().double(), groups, 1e-5)
+    tolerance = 1e-5 if dtype == "float32" else 1e-2
+    # Out of place, some rows only, in another order.
+    rows = [7, 0, 3]
+    out = torch.empty((3, width), dtype=kind, device=DEVICE)
+    held = on_device(stream)
+    kernels.stream_add_norm(held, (a_dev, b_dev), on_device(weight), 1e-5, out, rows=as_ints(rows), update=False, groups=groups, branch_scale=0.7)
+    assert relative_error(out.float().cpu(), wanted[rows]) < tolerance and torch.equal(held.cpu(), stream.float())
+    # In place: the stream takes the sum, the output its norm.
+    out = torch.empty((9, width), dtype=kind, device=DEVICE)
+    kernels.stream_add_norm(held, (a_dev, b_dev), on_device(weight), 1e-5, out, update=True, groups=groups, branch_scale=0.7)
+    assert relative_error(held.cpu(), summed) < 1e-6 and relative_error(out.float().cpu(), wanted) < tolerance
+    # No branch at all: the norm of the stream as it is.
+    kernels.stream_add_norm(held, None, on_device(weight), 1e-5, out, update=False, groups=groups)
+    assert relative_error(out.float().cpu(), wanted) < tolerance
+
+
+@pytest.mark.parametrize("width", [64, 100, 1030])
+def test_two_results_normalised_before_they_are_added(width):
+    generator = torch.Generator().manual_seed(width)
+    left, right, wl, wr = rand(generator, 7, width) * 3.0, rand(generator, 7, width) * 0.1, rand(generator, width), rand(generator, width)
+    out = torch.empty((7, width), dtype=torch.float32, device=DEVICE)
+    kernels.normed_pair_sum(on_device(left), on_device(right), on_device(wl), on_device(wr), 1e-5, 0.5, 0.25, out)
+    wanted = 0.5 * plain.unit_rms(left.float().double(), 1e-5) * wl.float().double() + 0.25 * plain.unit_rms(right.float().double(), 1e-5) * wr.float().double()
+    assert relative_error(out.cpu(), wanted) < 1e-5
+
+
+# ---- the matrix memory with a decay per key channel ----------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_token_shift_carries_the_last_input_from_step_to_step(dtype):
+    generator = torch.Generator().manual_seed(3)
+    width, mixes, kind = 70, 5, TORCH[dtype]
+    mu = torch.rand(mixes, width, dtype=F, generator=generator)
+    lengths = [9, 4, 13]
+    inputs = [rand(generator, length, width).to(kind).double() for length in lengths]
+    wanted = []
+    for x in inputs:
+        before = torch.cat([torch.zeros(1, width, dtype=F), x[:-1]])
+        wanted.append(torch.stack([x + (before - x) * mu[s].float().double() for s in range(mixes)]))
+    last = torch.zeros((6, width), dtype=torch.float32, device=DEVICE)
+    slots = [4, 1, 2]
+    last[3] = 7.0                                            # another sequence's: never read, never written
+    found = [[] for _ in lengths]
+    cursor = [0, 0, 0]
+    for runs in ([3, 1, 5], [1, 1, 1], [4, 0, 6], [1, 2, 1]):              # runs, single tokens (moved in the same launch), a sequence that pauses
+        live = [index for index, count in enumerate(runs) if count]
+        x = torch.cat([inputs[index][cursor[index] : cursor[index] + runs[index]] for index in live])
+        out = torch.empty((mixes, x.shape[0], width), dtype=kind, device=DEVICE)
+        kernels.token_shift(on_device(x, kind), on_device(mu), last, packed_step([runs[index] for index in live], [slots[index] for index in live]), out)
+        at = 0
+        for index in live:
+            found[index].append(out[:, at : at + runs[index]].double().cpu())
+            at += runs[index]
+            cursor[index] += runs[index]
+    for index in range(3):
+        assert cursor[index] == lengths[index]
+        assert relative_error(torch.cat(found[index], dim=1), wanted[index]) < (1e-6 if dtype == "float32" else 1e-2)
+    assert torch.all(last[3] == 7.0) and torch.all(last[0] == 0.0)
+    for index in range(3):
+        assert torch.equal(last[slots[index]].cpu().double(), inputs[index][-1])
+
+
+@pytest.mark.parametrize("heads, dim, vdim", [(3, 16, 16), (1, 20, 20), (5, 6, 6), (2, 24, 24), (4, 64, 64), (2, 100, 100), (2, 128, 128), (1, 40, 130), (37, 32, 32)])
+def test_the_matrix_memory_carries_its_state_from_step_to_step(heads, dim, vdim):
+    generator = torch.Generator().manual_seed(heads * 100 + dim)
+    lengths, slots = [37, 9, 20], [2, 5, 0]
+    state = torch.zeros((6, heads * vdim * dim), dtype=torch.float32, device=DEVICE)
+    state[3] = 5.0
+    bonus = rand(generator, heads, dim) * 0.5
+    data, wanted = [], []
+    for length in lengths:
+        r, k, v = rand(generator, length, heads, dim), rand(generator, length, heads, dim) * 0.5, rand(generator, length, heads, vdim)
+        pre, offset = rand(generator, length, heads * dim), rand(generator, heads * dim) - 1.0
+        data.append((r.float(), k.float(), v.float(), pre.float(), offset.float()))
+        w = torch.exp(-torch.exp(pre.float().double() + offset.float().double())).reshape(length, heads, dim)
+        wanted.append(plain.wkv_recurrence(r.float().double(), k.float().double(), v.float().double(), w, bonus.float().double()))
+    offset = data[0][4]
+    data = [(r, k, v, pre + (own - offset), offset) for r, k, v, pre, own in data]       # one offset for the layer, as a model has
+    found, cursor = [[] for _ in lengths], [0, 0, 0]
+    for runs in ([20, 1, 9], [1, 1, 1], [1, 1, 1], [15, 6, 9]):
+        parts = [[data[index][part][cursor[index] : cursor[index] + runs[index]].reshape(runs[index], -1) for index in range(3)] for part in range(4)]
+        r, k, v, pre = (on_device(torch.cat(part)) for part in parts)
+        kernels.channel_decay(pre, on_device(offset))
+        out = torch.empty((sum(runs), heads * vdim), dtype=torch.float32, device=DEVICE)
+        step = packed_step(runs, slots)
+        kernels.wkv(r, k, v, pre, on_device(bonus), state, step.cu_seqlens, step.seq_slot, out, heads, dim, vdim)
+        at = 0
+        for index in range(3):
+            found[index].append(out[at : at + runs[index]].cpu())
+            at += runs[index]
+            cursor[index] += runs[index]
+    for index in range(3):
+        assert relative_error(torch.cat(found[index]).reshape(lengths[index], heads, vdim), wanted[index]) < 2e-5
+    assert torch.all(state[3] == 5.0) and torch.all(state[1] == 0.0)
+
+
+def test_tanh_in_place():
+    values = torch.linspace(-6, 6, 1000, dtype=F).reshape(10, 100)
+    for kind, tolerance in ((torch.float32, 1e-6), (torch.bfloat16, 1e-2)):
+        held = on_device(values, kind)
+        kernels.tanh_(held)
+        assert relative_error(held.double().cpu(), torch.tanh(values.to(kind).double())) < tolerance
+
+
+# ---- the delta rule with a decay per key channel ---------------------------------------------------------------------------
+@pytest.mark.parametrize("heads, key_heads, dim, vdim", [(4, 2, 16, 24), (1, 1, 20, 70), (3, 3, 6, 34), (2, 1, 100, 10), (6, 6, 32, 32), (2, 2, 128, 64), (8, 4, 64, 130)])
+def test_the_delta_rule_with_a_decay_per_channel_carries_its_state(heads, key_heads, dim, vdim):
+    generator = torch.Generator().manual_seed(heads * 1000 + dim)
+    lengths, slots = [41, 7, 18], [3, 0, 4]
+    k_width, v_width = key_heads * dim, heads * vdim
+    a_log, dt_bias = rand(generator, heads) * 0.5 - 0.5, rand(generator, heads * dim) * 0.7
+    state = torch.zeros((6, heads * vdim * dim), dtype=torch.float32, device=DEVICE)
+    state[1] = 3.0
+    data, wanted = [], []
+    for length in lengths:
+        rows = rand(generator, length, 2 * k_width + v_width).float()
+        pre_beta, pre_step = rand(generator, length, heads).float(), rand(generator, length, heads * dim).float()
+        data.append((rows, pre_beta, pre_step))
+        q, k = rows[:, :k_width].double().reshape(length, key_heads, dim), rows[:, k_width : 2 * k_width].double().reshape(length, key_heads, dim)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dim ** -0.5
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+        per = heads // key_heads
+        step_size = plain.softplus(pre_step.double() + dt_bias.float().double()).reshape(length, heads, dim)
+        decay = torch.exp(-torch.exp(a_log.float().double())[None, :, None] * step_size)
+        wanted.append(plain.channel_gated_delta_rule(q.repeat_interleave(per, 1), k.repeat_interleave(per, 1), rows[:, 2 * k_width :].double().reshape(length, heads, vdim),
+                                                     torch.sigmoid(pre_beta.double()), decay))
+    found, cursor = [[] for _ in lengths], [0, 0, 0]
+    for runs in ([25, 1, 6], [1, 1, 1], [1, 1, 1], [14, 4, 10]):
+        rows, pre_beta, pre_step = (on_device(torch.cat([data[index][part][cursor[index] : cursor[index] + runs[index]] for index in range(3)])) for part in range(3))
+        tokens = sum(runs)
+        gates = torch.empty((tokens, heads, 2), dtype=torch.float32, device=DEVICE)
+        kq = torch.empty((tokens, key_heads), dtype=torch.float32, device=DEVICE)
+        kernels.delta_prepare(rows, 0, k_width, pre_beta, on_device(a_log), on_device(dt_bias), gates, kq, heads, key_heads, dim, pre_step)
+        out = torch.empty((tokens, v_width), dtype=torch.float32, device=DEVICE)
+        step = packed_step(runs, slots)
+        kernels.delta_rule(rows, 0, k_width, 2 * k_width, gates, kq, state, step.cu_seqlens, step.seq_slot, out, heads, key_heads, dim, vdim, pre_step)
+        at = 0
+        for index in range(3):
+            found[index].append(out[at : at + runs[index]].cpu())
+            at += runs[index]
+            cursor[index] += runs[index]
+    for index in range(3):
+        assert relative_error(torch.cat(found[index]).reshape(lengths[index], heads, vdim), wanted[index]) < 2e-5
+    assert torch.all(state[1] == 3.0) and torch.all(state[2] == 0.0)
+
+
+# ---- attention: sigmoid weights, the distance bias, gates, the temperature ---------------------------------------------
+def run_attention(kind_of, q, k, v, gate, dtype, page_of, heads_layout, extra, single_from):
+    """The attention kernels over pages that lie scattered: positions up to `single_from` in one run, the rest one token to a step
+    (the staged kernel).  q [tokens, heads, dim], k/v [tokens, kv_heads, dim or vdim] as the prepare kernel would have left them."""
+    kind = TORCH[dtype]
+    tokens, heads, dim = q.shape
+    kv_heads, vdim = k.shape[1], v.shape[2]
+    n_pages = max(page_of) + 2
+    if heads_layout:
+        rows = torch.full((n_pages, kv_heads, 64, dim), 9.0, dtype=kind, device=DEVICE)
+        values = torch.full((n_pages, kv_heads, 64, vdim), 9.0, dtype=kind, device=DEVICE)
+        for position in range(tokens):
+            rows[page_of[position // 64], :, position % 64] = on_device(k[position], kind)
+            values[page_of[position // 64], :, position % 64] = on_device(v[position], kind)
+    else:
+        rows = torch.full((n_pages, 64, kv_heads * (dim + vdim)), 9.0, dtype=kind, device=DEVICE)
+        values = None
+        for position in range(tokens):
+            rows[page_of[position // 64], position % 64] = on_device(torch.cat([k[position].reshape(-1), v[position].reshape(-1)]), kind)
+    pages = as_ints([page_of])
+    out = torch.empty((tokens, heads * vdim), dtype=kind, device=DEVICE)
+    for begin, end, staged in [(0, single_from, False)] + [(position, position + 1, True) for position in range(single_from, tokens)]:
+        step = SimpleNamespace(positions=as_ints(list(range(begin, end))), token_seq=as_ints([0] * (end - begin)))
+        kernels.masked_attention(on_device(q[begin:end], kind), rows, out[begin:end], step, pages, kv_heads, vdim, kind_of["scale"], value_pages=values, staged=staged,
+                                 gate=None if gate is None else on_device(gate[begin:end], kind), gate_per_head=kind_of.get("gate") == "head", **extra)
+    return out.float().cpu()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("heads, kv_heads, dim, vdim, heads_layout", [(4, 2, 16, 24, False), (1, 1, 12, 150, False), (9, 3, 10, 6, False), (6, 1, 96, 96, False),
+                                                                      (2, 1, 64, 64, True), (4, 2, 128, 128, True), (5, 5, 7, 3, False)])
+def test_sigmoid_weights_and_distance_biased_softmax_over_scattered_pages(dtype, heads, kv_heads, dim, vdim, heads_layout):
+    generator = torch.Generator().manual_seed(heads * 10 + dim)
+    tokens, kind = 200, TORCH[dtype]
+    rounded = lambda t: t.to(kind).double()
+    q, k, v = rounded(rand(generator, tokens, heads, dim)), rounded(rand(generator, tokens, kv_heads, dim)), rounded(rand(generator, tokens, kv_heads, vdim))
+    page_of = [5, 2, 7, 0]
+    tolerance = 2e-5 if dtype == "float32" else 2e-2
+    # Sigmoid weights with a number per head and a gate per head.
+    offset, gate = rand(generator, heads).float().double() - 1.0, rounded(rand(generator, tokens, heads))
+    wanted = plain.sigmoid_attention(q, k, v, dim ** -0.5, offset) * torch.sigmoid(gate)[:, :, None]
+    found = run_attention({"scale": dim ** -0.5, "gate": "head"}, q, k, v, gate, dtype, page_of, heads_layout,
+                          dict(sigmoid_weights=True, head_offset=on_device(offset)), single_from=140)
+    assert relative_error(found, wanted.reshape(tokens, -1)) < tolerance
+    # A softmax with the distance bias and a gate per element.
+    r1, r2 = torch.rand(heads, dtype=F, generator=generator).float().double(), 0.2 + torch.rand(heads, dtype=F, generator=generator).float().double()
+    gate = rounded(rand(generator, tokens, heads * vdim))
+    wanted = plain.distance_softmax_attention(q, k, v, dim ** -0.5, r1, r2).reshape(tokens, -1) * torch.sigmoid(gate)
+    found = run_attention({"scale": dim ** -0.5, "gate": "element"}, q, k, v, gate, dtype, page_of, heads_layout,
+                          dict(distance=on_device(torch.stack([r1, r2], dim=1))), single_from=140)
+    assert relative_error(found, wanted) < tolerance
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("far", [0, 63, 64, 127, 128, 318])          # the first position, both sides of two page borders, a key close by
+def test_one_key_far_back_that_stands_out_is_seen_by_both_attentions(dtype, far):
+    """Every key but one scores far below the rest: the query's result is that key's value (softmax) or that key's value alone counts
+    (sigmoid weights), wherever in the pages it lies; a lost or misplaced key gives another value."""
+    generator = torch.Generator().manual_seed(far)
+    tokens, dim, vdim = 320, 16, 8
+    direction = torch.zeros(dim, dtype=F)
+    direction[3] = 1.0
+    k = rand(generator, tokens, 1, dim) * 0.05
+    k[:, 0, 3] = -4.0                                    # along the query's direction every key scores very low ...
+    k[far, 0, 3] = 4.0                                   # ... but this one
+    q = (direction * 8.0).repeat(tokens, 1, 1).reshape(tokens, 1, dim)
+    v = rand(generator, tokens, 1, vdim)
+    page_of = [4, 1, 6, 3, 0]
+    softmax = run_attention({"scale": 1.0}, q, k, v, None, dtype, page_of, False, dict(distance=on_device(torch.tensor([[0.1, 0.5]], dtype=F))), single_from=300)
+    sigmoid = run_attention({"scale": 1.0}, q, k, v, None, dtype, page_of, False, dict(sigmoid_weights=True, head_offset=on_device(torch.tensor([-8.0], dtype=F))), single_from=300)
+    seen = TORCH[dtype]
+    for position in (far, 299, 300, 319):                # in the run and as a single token
+        if position >= far:
+            assert relative_error(softmax[position], v[far, 0].to(seen).double()) < 2e-2
+            assert relative_error(sigmoid[position], v[far, 0].to(seen).double()) < 2e-2
+    if far > 0:
+        assert float(sigmoid[far - 1].abs().max()) < 1e-3 * float(v.abs().max())       # before it, nothing weighs anything
+
+
+def test_the_query_temperature_and_the_queries_alone():
+    """The prepare kernel: queries times 1 + coef * ln(floor((p + 1) / every) + 1); with no keys of its own the layer writes none."""
+    generator = torch.Generator().manual_seed(8)
+    heads, kv_heads, dim, vdim, tokens = 3, 1, 10, 6, 50
+    projected = rand(generator, tokens, heads * dim + kv_heads * (dim + vdim)).float()
+    positions = list(range(100, 150))
+    rows = torch.full((4, 64, kv_heads * (dim + vdim)), 9.0, dtype=torch.float32, device=DEVICE)
+    pages = as_ints([[2, 0, 3, 1]])
+    queries = torch.empty((tokens, heads, dim), dtype=torch.float32, device=DEVICE)
+    kernels.masked_prepare(on_device(projected), None, None, 1e-5, None, 0, 1.0, queries, rows, as_ints(positions), as_ints([0] * tokens), pages, heads, kv_heads, dim, vdim,
+                           True, None, temperature=(0.3, 7))
+    factor = 1.0 + 0.3 * torch.log(torch.floor((torch.tensor(positions, dtype=F) + 1.0) / 7) + 1.0)
+    assert relative_error(queries.cpu().reshape(tokens, -1), projected[:, : heads * dim].double() * factor[:, None]) < 1e-6
+    assert torch.equal(rows[0, 100 - 64 : 150 - 64 if 150 <= 128 else 64].cpu(), projected[: 64 - (100 - 64), heads * dim :])      # positions 100..127 lie in page 0
+    assert torch.equal(rows[3, : 150 - 128].cpu(), projected[128 - 100 :, heads * dim :])
+    untouched = rows.clone()
+    kernels.masked_prepare(on_device(projected[:, : heads * dim]), None, None, 1e-5, None, 0, 1.0, queries, rows, as_ints(positions), as_ints([0] * tokens), pages, heads,
+                           kv_heads, dim, vdim, False, None)
+    assert torch.equal(rows, untouched) and relative_error(queries.cpu().reshape(tokens, -1), projected[:, : heads * dim]) < 1e-7
+
+
+# ---- routed experts with identity experts ----------------------------------------------------------------------------------
+@pytest.mark.parametrize("experts, identity, top, width, ff, tokens, dtype", [(5, 2, 3, 40, 24, 50, "float32"), (1, 0, 1, 40, 24, 50, "float32"), (1, 4, 2, 40, 24, 50, "float32"),
+                                                                              (3, 1, 4, 40, 24, 50, "float32"), (6, 3, 4, 64, 32, 9, "bfloat16"), (6, 3, 4, 64, 32, 300, "bfloat16")])
+def test_a_softmax_router_with_a_correction_and_identity_experts(experts, identity, top, width, ff, tokens, dtype):
+    """Few tokens take the streaming kernels, 300 tokens in bfloat16 the grouped tensor-core products; both against the plain statement."""
+    from tau_rs_b200.config.specs import RoutedExpertsSpec
+    from tau_rs_b200.parts.registry import build
+
+    generator = torch.Generator().manual_seed(experts * 10 + identity)
+    kind = TORCH[dtype]
+    mlp = {"kind": "moe", "router": {"experts": experts, "identity": identity, "top": top}, "expert": {"ff": ff}}
+    values = {"m.router": rand(generator, experts + identity, width) * 0.5, "m.correction": rand(generator, experts + identity) * 0.2}
+    for expert in range(experts):
+        values[f"m.e{expert}.gate"], values[f"m.e{expert}.up"] = rand(generator, ff, width) / width ** 0.5, rand(generator, ff, width) / width ** 0.5
+        values[f"m.e{expert}.down"] = rand(generator, width, ff) / ff ** 0.5
+    values = {name: value.to(torch.bfloat16).double() for name, value in values.items()}
+    h = rand(generator, tokens, width).to(kind).double()
+    part = build("feed_forward", RoutedExpertsSpec(hidden=width, intermediate=ff, experts=experts, top=top, score="softmax", correction=True, renormalize=False,
+                                                   identity=identity), prefix="m", dtype=kind, device=DEVICE)
+    for name, spec in part.tensor_specs().items():
+        part.assign(name, on_device(values[name], kind if spec.role == "matrix" else torch.float32))
+    part.finalize_weights()
+    found = part.forward(on_device(h, kind), SimpleNamespace(all_single=False)).double().cpu()
+    wanted = plain.routed_feed_forward(h, values, "m", mlp)
+    if dtype == "float32":
+        assert relative_error(found, wanted) < 2e-5
+    else:
+        rows = (found - wanted).abs().amax(dim=-1) / wanted.abs().max()
+        assert float(rows.median()) < 2e-2 and int((rows >= 6e-2).sum()) <= max(2, tokens // 10)      # a close call may choose another expert
+
+
+# ---- whole models: one mechanism to a model, then all together ----------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["only_attention", "only_shared_keys", "only_wkv", "only_parallel", "only_experts", "mixed", "odd", "many_groups"])
+def test_whole_prompts_single_tokens_and_the_first_positions(models, name, dtype):
+    engine, cfg, values = engine_of(models, name, dtype)
+    tokens = tokens_for(cfg, 200, 21)
+    wanted = plain_logits(cfg, values, tokens)
+    whole = run_whole(engine, tokens)
+    assert close(whole, wanted, dtype)
+    assert close(whole[:4], wanted[:4], dtype)               # the first tokens: zeros before the convolutions and the shift, empty states, one key
+    assert close(run_whole(engine, tokens[:1]), wanted[:1], dtype)
+    stepwise = run_tail_stepwise(engine, tokens, 199)                              # every token but the first alone, through the graphs
+    assert close(stepwise, wanted[1:], dtype)
+    if dtype == "float32":
+        assert relative_error(stepwise, whole[1:]) < 1e-5
+
+
+def test_the_residual_stream_after_every_layer(models):
+    """Layer by layer in 32-bit: the stream that the model hands from block to block, with what is still to join it, against the
+    plain statement's."""
+    folder, cfg, values = models["mixed"]
+    tokens = tokens_for(cfg, 90, 26)
+    _, layers = plain.forward(tokens, {name: value.double() for name, value in values.items()}, cfg, return_layers=True)
+    model = load_model(folder, "float32", "gpu")
+    engine = Engine(model, 256)
+    kept = []
+    for block in model.blocks:
+        original = block.forward
+
+        def recording(hidden, *args, _original=original, **kwargs):
+            stream, pending = _original(hidden, *args, **kwargs)
+            total = stream.double().cpu().clone()
+            for result in pending:
+                total += pending.scale * result.double().cpu()
+            kept.append(total)
+            return stream, pending
+
+        block.forward = recording
+    run_whole(engine, tokens)
+    assert len(kept) == len(cfg["layers"])
+    for index, (found, wanted) in enumerate(zip(kept, layers)):
+        assert relative_error(found, wanted) < 2e-5, index
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "long_memory", "heady"])
+def test_portions_down_to_two_tokens_and_page_borders(models, name, dtype):
+    engine, cfg, values = engine_of(models, name, dtype)
+    tokens = tokens_for(cfg, 330, 22)
+    wanted = plain_logits(cfg, values, tokens)
+    slot = engine.open_sequence()
+    found, position = [], 0
+    for count in [2, 2, 3, 56, 1, 1, 62, 2, 64, 1, 63, 2, 5, 64, 2]:               # runs that end at, before and behind positions 63/64, 127/128, ...
+        piece = tokens[position : position + count]
+        found.append(engine.step([StepEntry(slot, piece, list(range(count)))]).float().cpu().clone())
+        position += count
+    assert position == 330
+    engine.close_sequence(slot)
+    assert close(torch.cat(found), wanted, dtype)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["peaky", "heady"])
+def test_sharp_weights_lose_no_key_far_back_or_at_a_page_border(models, name, dtype):
+    engine, cfg, values = engine_of(models, name, dtype)
+    tokens = tokens_for(cfg, 400, 23)
+    wanted = plain_logits(cfg, values, tokens)
+    assert close(run_whole(engine, tokens), wanted, dtype)
+    tail = run_tail_stepwise(engine, tokens, 150)                                  # decoded queries cross page borders
+    assert close(tail, wanted[-150:], dtype)
+    slot = engine.open_sequence()                                                  # portions that read keys of earlier portions
+    found = [engine.step([StepEntry(slot, tokens[begin : begin + 50], list(range(50)))]).float().cpu().clone() for begin in range(0, 400, 50)]
+    engine.close_sequence(slot)
+    assert close(torch.cat(found), wanted, dtype)
+    shortened = plain_logits(cfg, values, tokens[64:])                             # the test would see keys that were lost
+    assert relative_error(shortened[-50:], wanted[-50:]) > 1e-3
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "heady"])
+def test_unequal_batches_against_each_request_alone(models, name, dtype):
+    engine, cfg, values = engine_of(models, name, dtype, 2048)
+    lengths, prompts = [90, 31, 140, 5, 66], [70, 1, 129, 3, 64]
+    requests = [tokens_for(cfg, length, 30 + index) for index, length in enumerate(lengths)]
+    together = run_batched(engine, requests, prompts)
+    for request, prompt, rows in zip(requests, prompts, together):
+        wanted = plain_logits(cfg, values, request)[prompt - 1 :]
+        assert close(rows, wanted, dtype)
+    engine.cache.check()
+    assert engine.cache.slots.in_use == 0
+
+
+def test_slots_pages_states_and_tails_that_are_used_again_start_clean(models):
+    """A cache of three pages and as many slots: every request takes a slot whose states, convolution tails and shifted inputs another
+    left behind, and pages that another wrote."""
+    engine, cfg, values = engine_of(models, "mixed", "float32", 64 * 3)
+    for round_number in range(4):
+        requests = [tokens_for(cfg, length, 40 + 3 * round_number + index) for index, length in enumerate([60 + round_number, 40, 17])]
+        together = run_batched(engine, requests, [len(request) - 6 for request in requests])
+        for request, rows in zip(requests, together):
+            assert relative_error(rows, plain_logits(cfg, values, request)[len(request) - 7 :]) < TOLERANCE["float32"]
+        engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_states_that_forget_slowly_over_long_decoding(models, dtype):
+    """Decays close to one: a state that was lost, restarted or carried by the wrong sequence shows hundreds of tokens later."""
+    engine, cfg, values = engine_of(models, "long_memory", dtype)
+    tokens = tokens_for(cfg, 420, 24)
+    wanted = plain_logits(cfg, values, tokens)
+    assert close(run_tail_stepwise(engine, tokens, 400), wanted[-400:], dtype)
+    shortened = plain_logits(cfg, values, tokens[100:])                            # the test would see a state that began later
+    assert relative_error(shortened[-50:], wanted[-50:]) > 1e-3
+
+
+def test_long_decoding_in_bfloat16_stays_with_the_plain_statement(models):
+    engine, cfg, values = engine_of(models, "mixed", "bfloat16")
+    tokens = tokens_for(cfg, 420, 24)
+    wanted = plain_logits(cfg, values, tokens)
+    assert close(run_tail_stepwise(engine, tokens, 400), wanted[-400:], "bfloat16")
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_greedy_generation_through_the_library_entry_point(models, name):
+    folder, cfg, values = models[name]
+    prompts = [tokens_for(cfg, length, 60 + index) for index, length in enumerate([9, 30, 2])]
+    output = generate(folder, prompts, max_new_tokens=12, dtype="float32", stop_tokens=[])
+    for prompt, result in zip(prompts, output):
+        tokens = list(prompt)
+        for _ in range(12):
+            logits = plain_logits(cfg, values, tokens)[-1]
+            best, second = torch.topk(logits, 2).values
+            if float(best - second) < 1e-3 * float(logits.abs().max()):
+                break                                                                # a close call proves nothing either way
+            tokens.append(int(torch.argmax(logits)))
+        made = len(tokens) - len(prompt)
+        assert list(result.tokens[:made]) == tokens[len(prompt) :] and made >= 1
+
+
+def test_trace_replay_of_a_nugolorn_folder(models, tmp_path):
+    folder, cfg, values = models["mixed"]                                            # the folder whose config.json leaves the ranks to the tensors
+    first, second = tokens_for(cfg, 70, 70), tokens_for(cfg, 33, 71)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": first[:66], "want": [0, 65]}, {"id": "b", "tokens": second[:30], "want": [29]}], "end": []}]
+    for index in range(3):
+        steps.append({"step": index + 1, "entries": [{"id": "a", "tokens": [first[66 + index]], "want": [0]}, {"id": "b", "tokens": [second[30 + index]], "want": [0]}],
+                      "end": ["b"] if index == 2 else []})
+    steps.append({"step": 4, "entries": [{"id": "a", "tokens": [first[69]], "want": []}], "end": ["a"]})
+    out = tmp_path / "out"
+    done = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out", str(out), "--max-tokens", "256"],
+                          input="\n".join(json.dumps(step) for step in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert done.returncode == 0, done.stderr[-2000:]
+    assert [line for line in done.stdout.split("\n") if line.startswith("done")] == [f"done {index}" for index in range(5)]
+    wanted_a, wanted_b = plain_logits(cfg, values, first), plain_logits(cfg, values, second)
+    rows = np.fromfile(out / "0.f32", dtype="<f4").reshape(3, cfg["vocab"])
+    assert relative_error(torch.from_numpy(rows), torch.stack([wanted_a[0], wanted_a[65], wanted_b[29]])) < TOLERANCE["float32"]
+    rows = np.fromfile(out / "3.f32", dtype="<f4").reshape(2, cfg["vocab"])
+    assert relative_error(torch.from_numpy(rows), torch.stack([wanted_a[68], wanted_b[32]])) < TOLERANCE["float32"]
+    assert not (out / "4.f32").exists()
+
+
+def test_the_command_line_on_a_nugolorn_folder(models, tmp_path):
+    """`bin/tau` on a Nugolorn folder: greedy tokens in 32-bit equal those of `generate()`, with graphs and without, in chunks of
+    prompt tokens; bfloat16 runs from the same folder; random weights are written for a Nugolorn config.json and read back."""
+    folder, cfg, values = models["mixed"]
+    prompts = [tokens_for(cfg, 40, 80), tokens_for(cfg, 7, 81)]
+    wanted = [list(result.tokens) for result in generate(folder, prompts, max_new_tokens=8, dtype="float32", stop_tokens=[])]
+
+    def run(arguments):
+        done = subprocess.run([os.path.join(ROOT, "bin", "tau")] + arguments, capture_output=True, text=True, timeout=900)
+        assert done.returncode == 0, done.stderr[-2000:]
+        return [json.loads(line) for line in done.stdout.splitlines() if line.startswith("{")]
+
+    base = ["--model", folder, "--max-tokens", "8", "--stop-ids", ""]
+    for prompt in prompts:
+        base += ["--prompt-ids", ",".join(str(token) for token in prompt)]
+    records = run(base + ["--dtype", "f32"])
+    assert [record["tokens"] for record in records if "tokens" in record] == wanted
+    records = run(base + ["--dtype", "f32", "--cuda-graph", "none", "--prefill-chunk-size", "16"])
+    assert [record["tokens"] for record in records if "tokens" in record] == wanted
+    records = run(base + ["--dtype", "bf16"])
+    assert all(len(record["tokens"]) == 8 for record in records if "tokens" in record)
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(nm.PEAKY))
+    drawn = str(tmp_path / "drawn")
+    records = run(["--random-weights", str(config_path), "--model", drawn, "--seed", "4", "--max-tokens", "5", "--stop-ids", "", "--prompt-ids", "1,2,3"])
+    assert [len(record["tokens"]) for record in records if "tokens" in record] == [5]
