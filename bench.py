@@ -339,9 +339,35 @@ def pegurax_sizes():
     }
 
 
+def nugolorn_sizes():
+    """Layer sizes that resemble a real model of Nugolorn's kind: an attention layer with sigmoid weights (128-element heads, 8 key/value
+    heads, 4 taps, half of each head rotated), a matrix memory with a decay per key channel (64 by 64 states, the decay through 64 numbers), a
+    softmax attention with a distance bias beside a gated delta rule with a decay per key channel (128 by 128 states, half as many key heads
+    as heads, 4 taps, decay and gate through 64 numbers), and an attention layer that reads the first one's keys and values; the
+    feed-forwards are dense, four times the width, or 32 experts and 4 identity experts of which 4 are chosen.  Beside it the closest
+    design that was here before, Pegurax (attention beside a delta rule, a recurrence, routed experts), and a dense Qwen3, each of the same
+    width, depth and vocabulary."""
+    def nugolorn(width, heads, expert_ff):
+        sigmoid = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4, "rot": {"base": 10000.0, "dims": 64}}
+        memory = {"heads": width // 64, "dim": 64, "decay_rank": 64}
+        left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.3, "every": 512}}
+        right = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}
+        dense, routed = {"kind": "dense", "ff": 4 * width}, {"kind": "moe", "router": {"experts": 32, "identity": 4, "top": 4}, "expert": {"ff": expert_ff}}
+        layers = [{"type": "attention", "mixer": sigmoid, "mlp": dense}, {"type": "wkv", "mixer": memory, "mlp": routed},
+                  {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense}, {"type": "attention", "mixer": dict(sigmoid, kv_from=0), "mlp": routed}]
+        return {"architecture": "Nugolorn", "layers": layers, "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.7, "logit_scale": 0.25, "vocab": 32768, "width": width}
+
+    pegurax = pegurax_sizes()
+    return {
+        "1024": (nugolorn(1024, 8, 704), pegurax["1024"][1], pegurax["1024"][0]),
+        "2048": (nugolorn(2048, 16, 1344), pegurax["2048"][1], pegurax["2048"][0]),
+        "4096": (nugolorn(4096, 32, 2752), pegurax["4096"][1], pegurax["4096"][0]),
+    }
+
+
 def design_comparison(args) -> int:
-    """`--design fasesun|bisudra|pegurax`: prefill and decode throughput of the design's layers at three real sizes beside a dense Qwen3
-    of equal width, depth and active feed-forward width (Pegurax also beside Fasesun), with the device time of each kernel class in one
+    """`--design fasesun|bisudra|pegurax|nugolorn`: prefill and decode throughput of the design's layers at three real sizes beside a dense Qwen3
+    of equal width, depth and active feed-forward width (Pegurax also beside Fasesun, Nugolorn also beside Pegurax), with the device time of each kernel class in one
     prompt step and one decode step."""
     import numpy as np
     import torch
@@ -357,7 +383,7 @@ def design_comparison(args) -> int:
     records = []
     clocks = ClockSampler()
     clocks.start()
-    sizes = {"bisudra": bisudra_sizes, "fasesun": fasesun_sizes, "pegurax": pegurax_sizes}[args.design]()
+    sizes = {"bisudra": bisudra_sizes, "fasesun": fasesun_sizes, "pegurax": pegurax_sizes, "nugolorn": nugolorn_sizes}[args.design]()
     for size, (design_config, dense_config, *others) in sizes.items():
         if args.widths and size not in args.widths.split(","):
             continue
@@ -420,7 +446,8 @@ def design_comparison(args) -> int:
                     mlp = layer.get("mlp")
                     if mlp and "router" in mlp:
                         experts, top = mlp["router"]["experts"], mlp["router"]["top"]
-                        distinct = experts * (1.0 - (1.0 - top / experts) ** batch)
+                        outputs = experts + mlp["router"].get("identity", 0)          # identity experts are chosen like the others and read nothing
+                        distinct = experts * (1.0 - (1.0 - top / outputs) ** batch)
                         read += int((distinct - top) * 3 * mlp["expert"]["ff"] * config["width"] * 2)
             record[label] = {
                 "prefill_tok_s": round(context / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
@@ -455,7 +482,7 @@ def main() -> int:
                         help="which measurements to run: prefill, decode, points, e2e, kernels (the counterparts of the reference arm's kernels), "
                              "classes (time per kernel class of a decode step, outside a graph)")
     parser.add_argument("--widths", default="", help="with --design: only these of the widths 1024, 2048, 4096 (comma-separated)")
-    parser.add_argument("--design", default="", choices=["", "fasesun", "bisudra", "pegurax"],
+    parser.add_argument("--design", default="", choices=["", "fasesun", "bisudra", "pegurax", "nugolorn"],
                         help="instead of the default workload: layers of this design at real sizes beside a dense Qwen3 of equal size")
     args = parser.parse_args()
 

@@ -31,15 +31,23 @@ class RMSNorm(Norm):
             raise KeyError(name)
         self.weight = tensor
 
+    def _options(self, branch) -> dict:
+        """What only some models ask of the kernel: pieces of the row normalised one by one, a factor on what joins the stream."""
+        groups, scale = getattr(self.spec, "groups", 1), getattr(branch, "scale", 1.0)
+        options = {} if groups == 1 else {"groups": groups}
+        if scale != 1.0:
+            options["branch_scale"] = scale
+        return options
+
     def forward(self, values, rows=None, branch=None):
         count = values.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((count, self.spec.width), dtype=self.dtype or values.dtype, device=values.device)
-        kernels.rms_norm(values, self.weight, self.spec.eps, out, rows, branch, getattr(self.spec, "groups", 1), getattr(branch, "scale", 1.0))
+        kernels.rms_norm(values, self.weight, self.spec.eps, out, rows, branch, **self._options(branch))
         return out
 
     def add_forward(self, branch, residual):
         out = torch.empty(residual.shape, dtype=self.dtype or residual.dtype, device=residual.device)
-        kernels.add_rms_norm(branch, residual, self.weight, self.spec.eps, out, getattr(self.spec, "groups", 1), getattr(branch, "scale", 1.0))
+        kernels.add_rms_norm(branch, residual, self.weight, self.spec.eps, out, **self._options(branch))
         return out
 
 

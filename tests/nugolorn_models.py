@@ -85,9 +85,9 @@ MANY_GROUPS = config([attention(mlp=None), wkv(mlp=None)], width=100, vocab=77, 
 PEAKY = config([parallel(softmax_side(heads=3, kv_heads=1, dim=16, vdim=24, scale=3.0, every=64), delta_side(heads=2, kv_heads=1, dim=8, vdim=8), mlp=None),
                 attention(heads=3, kv_heads=1, dim=16, vdim=24, scale=3.0, conv=2, rot_dims=16, mlp=None)], width=64, vocab=97, groups=2)
 # The same with keys and values as wide as ordinary heads (64 and 128), which the library keeps in another cache layout.
-HEADY = config([parallel(softmax_side(heads=2, kv_heads=1, dim=64, vdim=64, scale=2.0), delta_side(heads=2, kv_heads=1, dim=8, vdim=8), mlp=None),
-                attention(heads=2, kv_heads=2, dim=128, vdim=128, scale=1.0, conv=3, rot_dims=64, mlp=None),
-                attention(heads=4, kv_heads=2, dim=128, vdim=128, scale=1.0, conv=3, rot_dims=64, kv_from=1, mlp=None)], width=64, vocab=97, groups=4)
+HEADY = config([parallel(softmax_side(heads=2, kv_heads=1, dim=64, vdim=64, scale=0.5), delta_side(heads=2, kv_heads=1, dim=8, vdim=8), mlp=None),
+                attention(heads=2, kv_heads=2, dim=128, vdim=128, scale=0.25, conv=3, rot_dims=64, mlp=None),
+                attention(heads=4, kv_heads=2, dim=128, vdim=128, scale=0.25, conv=3, rot_dims=64, kv_from=1, mlp=None)], width=64, vocab=97, groups=4)
 # Recurrences only slowly forgetting, so that a state lost or restarted shows hundreds of tokens later.
 LONG_MEMORY = config([parallel(softmax_side(heads=2, kv_heads=2, dim=8, vdim=8), delta_side(heads=4, kv_heads=1, dim=32, vdim=16, conv=4), mlp=None),
                       wkv(heads=2, dim=32, rank=4, mlp=None)], width=64, vocab=53, groups=2)
