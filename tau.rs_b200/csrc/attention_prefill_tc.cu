@@ -12,6 +12,11 @@
 //                 bfloat16 and written over the row's scores in tensor memory
 //   O += P V      tcgen05.mma, A = P from tensor memory, B = value tile as it lies (`[key][d]`, MN-major)
 //
+// A second form of the kernel (`kExtended`, chosen by the launcher where a caller asks for any of this) serves other weights: a bias that
+// falls with the logarithm of the distance, `- r1 log(1 + r2 (i - j))` with two numbers per head, enters the scores before the maximum
+// (in the exponent's base-2 scale, one `lg2.approx` a score); sigmoid weights `sigmoid(score + offset[head])` replace the softmax (no
+// maximum, no sum, no rescaling: every probability stands alone); and a gate per (token, head) multiplies the row as it leaves.
+//
 // The accumulator O is rescaled only when a row's maximum has grown by more than 2^8 since the last rescale, so most
 // tiles do not touch it; the final division by the row sum makes the result exact either way.  The score products run
 // one tile ahead of the softmax (two score buffers in tensor memory), so the tensor cores work on tile i + 1 and on the
@@ -280,12 +285,14 @@ __device__ __forceinline__ Span span_of(const Item& item, int window, int chunk)
     return span;
 }
 
+template <bool kExtended>
 __global__ void __launch_bounds__(kThreads, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                             const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap out_map, bf16* __restrict__ out,
                             const int* __restrict__ cu_seqlens, const int* __restrict__ seq_start, const int* __restrict__ page_rows,
                             int page_stride, int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, int chunk, int sink,
-                            float out_scale, long long out_stride, int n_items, int* __restrict__ schedule) {
+                            float out_scale, long long out_stride, int n_items, int* __restrict__ schedule, const float* __restrict__ distance,
+                            int sigmoid_weights, const float* __restrict__ head_offset, const bf16* __restrict__ head_gate, long long gate_stride) {
     extern __shared__ uint8_t shared_raw[];
     uint8_t* tiles = shared_raw;                                   // the swizzled tiles need 1,024-byte alignment
     uint8_t* q_tile = tiles;                                       // kHalves slices of [128 rows x 128 bytes]
@@ -532,6 +539,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             // there, when its own work on the next is over), so the epilogue reads it again and the loop carries less.
             const volatile Item* item_place = &shared->item[k & 1];
             int n_tiles, first_tile, last_position, position0;
+            float far = 0.0f, reach = 0.0f, offset_log2 = 0.0f;     // the head's distance numbers and its offset (extended form)
+            if (kExtended) {
+                const int head = item_place->head;
+                if (distance) far = distance[2 * head], reach = distance[2 * head + 1];
+                if (head_offset) offset_log2 = head_offset[head] * 1.4426950408889634f;
+            }
+            const bool biased = kExtended && distance != nullptr, sigmoid = kExtended && sigmoid_weights != 0;
+            const float tile_scale = biased ? 1.0f : scale_log2;    // biased scores are brought to the exponent's scale with the bias
             {
                 Item item;
                 item.seq = item_place->seq, item.rows_here = item_place->rows_here, item.position0 = item_place->position0;
@@ -584,6 +599,14 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 const bool bounded = window > 0 || chunk > 0;
                 const bool all_seen = key0 + BN - 1 <= warp_first && (!bounded || key0 >= first_seen(warp_last, window, chunk));
                 const bool none_seen = key0 > warp_last || (bounded && key0 + BN - 1 < first_seen(warp_first, window, chunk));
+                if (biased && !none_seen) {
+                    // score * scale * log2(e) - r1 * log2(1 + r2 * distance); keys behind the query (masked below) count as distance 0.
+#pragma unroll
+                    for (int j = 0; j < BN; ++j) {
+                        const int apart = position - key0 - j;
+                        score[j] = fmaf(score[j], scale_log2, -far * __log2f(fmaf(reach, static_cast<float>(apart > 0 ? apart : 0), 1.0f)));
+                    }
+                }
                 if (!all_seen && !none_seen) {
                     const int highest = position - key0;
                     if (bounded) {
@@ -596,12 +619,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     }
                 }
                 float tile_max = -INFINITY;
-                if (!none_seen) {
+                if (!none_seen && !sigmoid) {
                     float partial_max[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                     for (int j = 0; j < BN; j += 2) partial_max[(j >> 1) & 3] = max_of_three(partial_max[(j >> 1) & 3], score[j], score[j + 1]);
                     // Of the raw scores; the scale is positive and is applied afterwards.
-                    tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3])) * scale_log2;
+                    tile_max = fmaxf(fmaxf(partial_max[0], partial_max[1]), fmaxf(partial_max[2], partial_max[3])) * tile_scale;
                 }
                 // Rescale O and the sum only when the maximum has grown by more than the threshold (or nothing was kept yet).
                 float shift = used_max;
@@ -654,7 +677,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     tensor_store_words_16(lane_base + (tile & 1) * BN + 16, zeros);
                 } else {
                     Float2 partial_sum[4] = {pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f)};
-                    const Float2 scale_pair = pair_of(scale_log2, scale_log2), shift_pair = pair_of(-subtract, -subtract);
+                    // Sigmoid weights: 1 / (1 + 2^-(score + offset)) with both in the base-2 scale; a masked score of -inf gives 1 / inf = 0.
+                    const float added = sigmoid ? -offset_log2 : -subtract, factor = sigmoid ? -tile_scale : tile_scale;
+                    const Float2 scale_pair = pair_of(factor, factor), shift_pair = pair_of(added, added);
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {   // 32 keys are 16 columns
                         uint32_t packed[16];
@@ -662,7 +687,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                         for (int j = 0; j < 32; j += 2) {
                             float x0, x1;
                             unpair(fma_pair(pair_of(score[half * 32 + j], score[half * 32 + j + 1]), scale_pair, shift_pair), x0, x1);
-                            const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+                            if (sigmoid) p0 = __frcp_rn(1.0f + p0), p1 = __frcp_rn(1.0f + p1);
                             partial_sum[(j >> 1) & 3] = add_pair(partial_sum[(j >> 1) & 3], pair_of(p0, p1));
                             packed[j / 2] = pack_bf16(p0, p1);
                         }
@@ -683,7 +709,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             tensor_fence_after_sync();
             // With a sink the denominator has the weight of a key with score 0 and no value added: exp2(0 - used_max) in the sums' scale.
             // Where that overflows every key's weight is nothing beside it, and the row is zero.
-            const float inverse = out_scale / (sink ? sum + exp2f(-used_max) : sum);
+            float inverse = sigmoid ? out_scale : out_scale / (sink ? sum + exp2f(-used_max) : sum);
+            if (kExtended && head_gate && row < item_place->rows_here)      // one gate per (token, head) on the whole row
+                inverse /= 1.0f + expf(-__bfloat162float(head_gate[static_cast<size_t>(item_place->row + row) * gate_stride + item_place->head]));
             // Every product of the item is done, so the place of the value tiles is free (the next item's first value tile
             // waits for `staged`): the rows go there as bfloat16 in the layout of the copy engine's swizzled tiles (slices of
             // 64 elements, rows of 128 bytes, the 16-byte pieces of a row exchanged by the row's number, which also keeps
@@ -802,8 +830,10 @@ TAU_EXPORT int tau_attention_prefill_tc_status() {
 TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, const void* values, void* out, const int* cu_seqlens,
                                         const int* seq_start, const int* page_rows, int page_stride, int page_tokens, long long n_pages,
                                         int n_seqs, int n_tokens, int n_heads, int n_kv_heads, float scale, int window, int chunk, int sink,
-                                        float out_scale, long long out_stride, int* schedule, void* stream) {
+                                        float out_scale, long long out_stride, int* schedule, const float* distance, int sigmoid_weights,
+                                        const float* head_offset, const void* head_gate, long long gate_stride, void* stream) {
     if (n_tokens <= 0 || n_seqs <= 0) return 0;
+    if (sigmoid_weights && sink) return cudaErrorInvalidValue;
     if (!queries || !keys || !values || !out || !cu_seqlens || !seq_start || !page_rows || !schedule || n_heads <= 0 || n_kv_heads <= 0 ||
         n_heads % n_kv_heads != 0 || page_tokens != BN || window < 0 || chunk < 0 || (window > 0 && chunk > 0) || n_pages <= 0 ||
         out_stride < static_cast<long long>(n_heads) * D || out_stride % 8 != 0 || (reinterpret_cast<uintptr_t>(out) & 15u) != 0)
@@ -817,7 +847,8 @@ TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, c
     const int shared_bytes = kQBytes + (kKeyStages + kValueStages) * kKeyBytes + static_cast<int>(sizeof(Shared));
     static int places = 0;   // blocks that the device holds at once
     if (!places) {
-        cudaError_t status = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
+        cudaError_t status = cudaFuncSetAttribute(attention_prefill_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
+        if (status == cudaSuccess) status = cudaFuncSetAttribute(attention_prefill_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, shared_bytes);
         if (status != cudaSuccess) return static_cast<int>(status);
         // Two blocks to an SM: the kernel is compiled for that many (registers), tensor memory holds the columns of two,
         // and a block's shared memory (plus the kilobyte that the system keeps for each) fits twice.
@@ -832,8 +863,10 @@ TAU_EXPORT int tau_attention_prefill_tc(const void* queries, const void* keys, c
     const long long items = (static_cast<long long>((n_tokens + BM - 1) / BM) + n_seqs) * n_heads;   // every sequence may leave a ragged tile
     if (items > 0x7fffffffLL) return cudaErrorInvalidValue;
     const int blocks = static_cast<int>(items < places ? items : places);
-    tau_launch(attention_prefill_tc_kernel, dim3(blocks), dim3(kThreads), shared_bytes, static_cast<cudaStream_t>(stream), q_map, k_map, v_map,
-               out_map, static_cast<bf16*>(out), cu_seqlens, seq_start, page_rows, page_stride, n_seqs, n_tokens, n_heads, n_kv_heads, scale,
-               window, chunk, sink, out_scale, out_stride, static_cast<int>(items), schedule);
+    const bool extended = distance || sigmoid_weights || head_offset || head_gate;
+    tau_launch(extended ? attention_prefill_tc_kernel<true> : attention_prefill_tc_kernel<false>, dim3(blocks), dim3(kThreads), shared_bytes,
+               static_cast<cudaStream_t>(stream), q_map, k_map, v_map, out_map, static_cast<bf16*>(out), cu_seqlens, seq_start, page_rows, page_stride, n_seqs,
+               n_tokens, n_heads, n_kv_heads, scale, window, chunk, sink, out_scale, out_stride, static_cast<int>(items), schedule, distance, sigmoid_weights,
+               head_offset, static_cast<const bf16*>(head_gate), gate_stride);
     return tau_launch_status();
 }

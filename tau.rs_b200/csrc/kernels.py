@@ -87,7 +87,7 @@ _CLASS_OF = {
     "moe_combine": "routing", "diff_prepare": "attention", "diff_attention": "attention", "diff_combine": "attention", "causal_taps": "norm", "gated_add_norm": "norm",
     "side_gate": "activation", "unit_add_mix": "norm", "norm_rows": "norm", "relu_squared": "activation",
     "short_conv": "recurrence", "delta_prepare": "recurrence", "delta_rule": "recurrence", "selective_scan": "recurrence",
-    "masked_prepare": "attention", "masked_attention": "attention",
+    "masked_prepare": "attention", "masked_attention": "attention", "gated_rows": "attention",
     "token_shift": "recurrence", "tanh": "activation", "channel_decay": "recurrence", "wkv": "recurrence",
 }
 _timing = None     # while timing: [last event, [(class, event after the launch), ...]]
@@ -698,12 +698,22 @@ _prefill_schedule = {}   # (device, stream) -> the two counters by which the blo
 
 
 def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page_rows, n_heads: int, n_kv_heads: int, head_dim: int,
-                         scale: float, window: int, chunk: int = 0, sink: bool = False, out_scale: float = 1.0) -> None:
+                         scale: float, window: int, chunk: int = 0, sink: bool = False, out_scale: float = 1.0, distance=None, sigmoid_weights: bool = False,
+                         head_offset=None, head_gate=None) -> None:
     """The same as `attention_prefill` on the tcgen05 tensor cores (accumulators in tensor memory); head sizes 64 and 128.
     Beyond it: with `chunk` a query sees only the keys of its own chunk of `chunk` positions (counted from position 0 of the
     sequence) instead of a window; with `sink` the softmax's denominator has one added; the result is multiplied by `out_scale`;
-    `out` may be a column range of a wider tensor whose rows start on 16-byte borders."""
-    _on_device(queries, keys, values, out, cu_seqlens, seq_start, page_rows)
+    `out` may be a column range of a wider tensor whose rows start on 16-byte borders.  `distance` (float32 [n_heads, 2] = (r1, r2)):
+    `r1 * ln(1 + r2 * (i - j))` is taken off the score of key j for the query at i.  `sigmoid_weights`: every visible key weighs
+    `sigmoid(score + head_offset[head])` (float32 [n_heads] or None) instead of its share of a softmax.  `head_gate` (bfloat16
+    [tokens, n_heads], rows any distance apart): a head's result is multiplied by the sigmoid of its number."""
+    _on_device(queries, keys, values, out, cu_seqlens, seq_start, page_rows, distance, head_offset, head_gate)
+    if distance is not None:
+        _require(distance.dtype == torch.float32 and distance.shape == (n_heads, 2) and distance.is_contiguous(), "the distance numbers must be float32 [heads, 2]")
+    _f32_vector(head_offset, n_heads, "the heads' offsets")
+    _require(not (sigmoid_weights and sink), "sigmoid weights have no denominator for a sink to join")
+    if head_gate is not None:
+        _require(head_gate.dtype == torch.bfloat16 and head_gate.shape == (queries.shape[0], n_heads) and head_gate.stride(1) == 1, "the gate must be bfloat16 [tokens, heads]")
     tokens = queries.shape[0]
     n_seqs = seq_start.numel()
     _require(head_dim in (64, 128), "the tensor-core prefill kernel serves head sizes 64 and 128")
@@ -727,8 +737,9 @@ def attention_prefill_tc(queries, keys, values, out, cu_seqlens, seq_start, page
         _pointer(queries), _pointer(keys), _pointer(values), _pointer(out), _pointer(cu_seqlens), _pointer(seq_start), _pointer(page_rows),
         ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_longlong(keys.shape[0]), ctypes.c_int(n_seqs),
         ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk),
-        ctypes.c_int(1 if sink else 0), ctypes.c_float(out_scale), ctypes.c_longlong(out.stride(0)), _pointer(schedule), _stream()),
-        "attention_prefill_tc")
+        ctypes.c_int(1 if sink else 0), ctypes.c_float(out_scale), ctypes.c_longlong(out.stride(0)), _pointer(schedule), _pointer(distance),
+        ctypes.c_int(1 if sigmoid_weights else 0), _pointer(head_offset), _pointer(head_gate), ctypes.c_longlong(0 if head_gate is None else head_gate.stride(0)),
+        _stream()), "attention_prefill_tc")
 
 
 def attention_prefill_tc_status(head_dim: int) -> int:
@@ -1256,6 +1267,7 @@ def selective_scan(x, z, pre, bc, a_log, skip, state, cu_seqlens, seq_slot, out)
 
 # ---------------------------------------------------------------------------- attention over cached rows with a mask and a sink
 MASKED_MAX_VALUE_DIM = 512
+MASKED_STAGED_WARPS = 4      # query heads of a key/value head that one block of the staged kernel serves
 
 
 def masked_prepare(projected, q_weight, k_weight, eps: float, frequency, rotary_dim: int, magnitude: float, queries, rows, positions, token_seq,
@@ -1306,7 +1318,7 @@ def _require_masked_pages(rows, value_pages, dtype, n_kv_heads: int, dim: int, v
 
 def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim: int, scale: float, window: int = 0, chunk: int = 0, sink: bool = False,
                      out_scale: float = 1.0, value_pages=None, staged: bool = False, distance=None, sigmoid_weights: bool = False, head_offset=None,
-                     gate=None, gate_per_head: bool = False) -> None:
+                     gate=None, gate_per_head: bool = False, splits: int = 1) -> None:
     """Causal softmax attention of every token over the cached rows of its sequence: within `window` positions (if not 0), or
     within the token's own chunk of `chunk` positions counted from position 0 (if not 0); with `sink` the softmax's denominator has
     one added.  `out` [tokens, n_heads * vdim] (rows any distance apart) receives the result times `out_scale`.  Scores, weights
@@ -1316,7 +1328,8 @@ def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim:
     (r1, r2)): `r1 * ln(1 + r2 * (i - j))` is taken off the score of key j for the query at i.  `sigmoid_weights`: instead of a
     softmax every visible key weighs `sigmoid(score + head_offset[head])` (float32 [n_heads] or None), not normalised.  `gate`
     ([tokens, n_heads] with `gate_per_head`, else [tokens, n_heads * vdim]; the queries' dtype; rows any distance apart): the result
-    is multiplied by its sigmoid."""
+    is multiplied by its sigmoid.  `splits` > 1 (with `staged`): every token's context is cut into that many ranges that as many
+    blocks walk, and a second launch joins them."""
     _on_device(queries, rows, out, page_rows, value_pages, distance, head_offset, gate)
     tokens, n_heads, dim = queries.shape
     if distance is not None:
@@ -1332,13 +1345,26 @@ def masked_attention(queries, rows, out, step, page_rows, n_kv_heads: int, vdim:
     _require(vdim <= MASKED_MAX_VALUE_DIM, f"values may have at most {MASKED_MAX_VALUE_DIM} elements per head")
     _require(not (window and chunk), "a window or a chunk, not both")
     _require(page_rows.dtype == torch.int32 and page_rows.dim() == 2 and page_rows.is_contiguous(), "page rows must be int32 [sequences, stride]")
+    splits = max(1, min(int(splits), 64)) if staged else 1
+    partial = torch.empty((tokens, n_heads, splits, vdim + 2), dtype=torch.float32, device=queries.device) if splits > 1 else None
     library = build.load_library("masked_attention.cu")
     _check(library.tau_masked_attention(
         _code(queries), _pointer(queries), _pointer(rows), _pointer(value_pages), _pointer(out), ctypes.c_longlong(out.stride(0)), _pointer(step.positions), _pointer(step.token_seq),
         _pointer(page_rows), ctypes.c_int(page_rows.shape[1]), ctypes.c_int(PAGE_TOKENS), ctypes.c_int(tokens), ctypes.c_int(n_heads), ctypes.c_int(n_kv_heads),
         ctypes.c_int(dim), ctypes.c_int(vdim), ctypes.c_float(scale), ctypes.c_int(window), ctypes.c_int(chunk), ctypes.c_int(1 if sink else 0),
         ctypes.c_float(out_scale), ctypes.c_int(1 if staged else 0), _pointer(distance), ctypes.c_int(1 if sigmoid_weights else 0), _pointer(head_offset),
-        _pointer(gate), ctypes.c_longlong(0 if gate is None else gate.stride(0)), ctypes.c_int(1 if gate_per_head else 0), _stream()), "masked_attention")
+        _pointer(gate), ctypes.c_longlong(0 if gate is None else gate.stride(0)), ctypes.c_int(1 if gate_per_head else 0), ctypes.c_int(splits), _pointer(partial),
+        _stream()), "masked_attention", 2 if splits > 1 else 1)
+
+
+def gated_rows(values, gate, out) -> None:
+    """`out = values * sigmoid(gate)`, element by element; [rows, width] of one dtype, rows any distance apart; `out` may be `values`."""
+    _on_device(values, gate, out)
+    _require(values.shape == gate.shape == out.shape and values.dim() == 2 and values.dtype == gate.dtype == out.dtype
+             and values.stride(1) == gate.stride(1) == out.stride(1) == 1, "values, gate and output must be [rows, width] of one dtype")
+    library = build.load_library("masked_attention.cu")
+    _check(library.tau_sigmoid_gate(_code(values), _pointer(values), ctypes.c_longlong(values.stride(0)), _pointer(gate), ctypes.c_longlong(gate.stride(0)), _pointer(out),
+                                    ctypes.c_longlong(out.stride(0)), ctypes.c_int(values.shape[0]), ctypes.c_int(values.shape[1]), _stream()), "gated_rows")
 
 
 # ---------------------------------------------------------------------------- a matrix state with a decay per key channel and a bonus

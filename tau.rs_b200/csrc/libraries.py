@@ -21,6 +21,7 @@ def all_libraries() -> List[Tuple[str, Sequence[str]]]:
         ("masked_attention.cu", ()),
         ("short_conv.cu", ()),
         *[("delta_rule.cu", (f"TAU_KEY_DIM={key_dim}",)) for key_dim in (16, 32, 64, 128)],
+        *[("wkv.cu", (f"TAU_KEY_DIM={key_dim}",)) for key_dim in (16, 32, 64)],
         *[("selective_scan.cu", (f"TAU_SCAN_STATES={states}",)) for states in (8, 16, 32)],
         *[("recurrence.cu", (f"TAU_KEY_DIM={key_dim}",)) for key_dim in (16, 32, 64, 128)],
         # Specialised libraries: the head sizes of the benchmark shape and of the tests' tiny models.

@@ -219,6 +219,9 @@ masked_attention_kernel(const T* __restrict__ queries, const T* __restrict__ row
 // aligned because dim and vdim are multiples of a word's elements), two tiles deep, so that the group's heads share one pass over
 // the cache and the loads are whole rows.  Key rows are an odd number of words apart: lane j reads key j without bank conflicts.
 // Then as above: a lane scores one key, every lane sums its own value columns; maximum, weights and sums in 32-bit.
+// With `splits` > 1 the grid's z cuts a token's tiles into that many ranges, a block leaves its range's sums, maximum and denominator
+// in `partial` ([tokens, heads, splits, vdim + 2] floats), and `masked_attention_merge_kernel` joins them: few tokens over a long
+// context then fill the machine.
 constexpr int kStagedWarps = 4;
 constexpr int kTileKeys = 32;
 
@@ -248,7 +251,7 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
                                long long out_stride, const int* __restrict__ positions, const int* __restrict__ token_seq, const int* __restrict__ page_rows,
                                int page_stride, int page_tokens, int heads, int kv_heads, int dim, int vdim, float scale, int window, int chunk, int sink,
                                float out_scale, const float* __restrict__ distance, int sigmoid_weights, const float* __restrict__ head_offset,
-                               const T* __restrict__ gate, long long gate_stride, int gate_per_head) {
+                               const T* __restrict__ gate, long long gate_stride, int gate_per_head, int splits, float* __restrict__ partial) {
     grid_dependents_launch();
     grid_dependency_wait();
     constexpr int kPer = Word<T>::kElements;
@@ -276,7 +279,11 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
     int first_key = 0;
     if (window > 0 && position - window + 1 > 0) first_key = position - window + 1;
     if (chunk > 0) first_key = position / chunk * chunk;
-    const int n_tiles = (position - first_key) / kTileKeys + 1;
+    const int all_tiles = (position - first_key) / kTileKeys + 1;
+    // This block's range of the token's tiles (all of them without splits); tiles are numbered from the range's first.
+    const int per_split = (all_tiles + splits - 1) / splits, tile_begin = static_cast<int>(blockIdx.z) * per_split;
+    const int n_tiles = all_tiles - tile_begin < per_split ? (all_tiles - tile_begin > 0 ? all_tiles - tile_begin : 0) : per_split;
+    first_key += tile_begin * kTileKeys;
 
     auto stage = [&](int tile) {
         uint32_t* buffer = staged_words + (tile & 1) * tile_words;
@@ -303,7 +310,8 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
     const float* query = query_rows + warp * dim;
     const float far = distance ? distance[2 * head] : 0.0f, reach = distance ? distance[2 * head + 1] : 0.0f;
     const float offset = head_offset ? head_offset[head] : 0.0f;
-    float top = sink ? 0.0f : -INFINITY, sum = sink ? 1.0f : 0.0f;
+    const bool with_sink = sink && blockIdx.z == 0;      // the added one is counted once
+    float top = with_sink ? 0.0f : -INFINITY, sum = with_sink ? 1.0f : 0.0f;
     float acc[kMaxOwned];
 #pragma unroll
     for (int i = 0; i < kMaxOwned; ++i) acc[i] = 0.0f;
@@ -357,6 +365,19 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
     }
     copy_wait<0>();
     if (!has_head) return;
+    if (partial) {      // this range's sums as they stand (in the scale of its own maximum), then the maximum and the denominator
+        float* record = partial + ((static_cast<size_t>(token) * heads + head) * splits + blockIdx.z) * (vdim + 2);
+#pragma unroll
+        for (int i = 0; i < kMaxOwned / kPer; ++i) {
+            const int word = lane + 32 * i;
+            if (word < value_words) {
+#pragma unroll
+                for (int e = 0; e < kPer; ++e) record[word * kPer + e] = acc[i * kPer + e];
+            }
+        }
+        if (lane == 0) record[vdim] = top, record[vdim + 1] = sum;
+        return;
+    }
     const float factor = sigmoid_weights ? out_scale : out_scale / sum;
     T* target = out + static_cast<size_t>(token) * out_stride + head * vdim;
     const T* gates = gate ? gate + static_cast<size_t>(token) * gate_stride + (gate_per_head ? head : head * vdim) : nullptr;
@@ -374,6 +395,37 @@ masked_attention_staged_kernel(const T* __restrict__ queries, const T* __restric
     }
 }
 
+// grid (tokens, heads); block 128.  Joins the ranges that the staged kernel left in `partial`: the sums are brought to the largest
+// maximum and added, divided by the joined denominator (sigmoid weights: added as they are), gated and rounded once.
+template <typename T>
+__global__ void __launch_bounds__(128)
+masked_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__ out, long long out_stride, int heads, int vdim, int splits, float out_scale,
+                              int sigmoid_weights, const T* __restrict__ gate, long long gate_stride, int gate_per_head) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const int token = blockIdx.x, head = blockIdx.y;
+    const float* records = partial + (static_cast<size_t>(token) * heads + head) * splits * (vdim + 2);
+    float top = -INFINITY;
+    if (!sigmoid_weights)
+        for (int split = 0; split < splits; ++split) top = fmaxf(top, records[static_cast<size_t>(split) * (vdim + 2) + vdim]);
+    float total = 0.0f;
+    if (!sigmoid_weights)
+        for (int split = 0; split < splits; ++split)
+            total += records[static_cast<size_t>(split) * (vdim + 2) + vdim + 1] * expf(records[static_cast<size_t>(split) * (vdim + 2) + vdim] - top);
+    const float factor = sigmoid_weights ? out_scale : out_scale / total;
+    const T* gates = gate ? gate + static_cast<size_t>(token) * gate_stride + (gate_per_head ? head : head * vdim) : nullptr;
+    for (int column = threadIdx.x; column < vdim; column += blockDim.x) {
+        float sum = 0.0f;
+        for (int split = 0; split < splits; ++split) {
+            const float* record = records + static_cast<size_t>(split) * (vdim + 2);
+            sum += sigmoid_weights ? record[column] : record[column] * expf(record[vdim] - top);      // a range without keys: exp(-inf) = 0
+        }
+        float value = sum * factor;
+        if (gates) value /= 1.0f + expf(-to_float(gates[gate_per_head ? 0 : column]));
+        out[static_cast<size_t>(token) * out_stride + head * vdim + column] = from_float<T>(value);
+    }
+}
+
 // Shared memory of the staged kernel, or 0 where it does not serve these sizes.
 template <typename T>
 int staged_bytes(int dim, int vdim) {
@@ -387,7 +439,7 @@ template <typename T>
 int launch_staged(int bytes, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
                   const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads, int dim, int vdim,
                   float scale, int window, int chunk, int sink, float out_scale, const float* distance, int sigmoid_weights, const float* head_offset,
-                  const void* gate, long long gate_stride, int gate_per_head, cudaStream_t s) {
+                  const void* gate, long long gate_stride, int gate_per_head, int splits, float* partial, cudaStream_t s) {
     static int allowed = 48 * 1024;
     if (bytes > allowed) {
         cudaError_t status = cudaFuncSetAttribute(masked_attention_staged_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
@@ -395,14 +447,47 @@ int launch_staged(int bytes, const void* queries, const void* rows, const void* 
         allowed = 160 * 1024;
     }
     const int group_size = heads / kv_heads, passes = (group_size + kStagedWarps - 1) / kStagedWarps;
-    tau_launch(masked_attention_staged_kernel<T>, dim3(tokens, kv_heads * passes), dim3(kStagedWarps * 32), bytes, s, static_cast<const T*>(queries),
+    if (splits > 1 && !partial) return cudaErrorInvalidValue;
+    if (splits <= 1) splits = 1, partial = nullptr;
+    tau_launch(masked_attention_staged_kernel<T>, dim3(tokens, kv_heads * passes, splits), dim3(kStagedWarps * 32), bytes, s, static_cast<const T*>(queries),
                static_cast<const T*>(rows), static_cast<const T*>(value_pages), static_cast<T*>(out), out_stride, positions, token_seq, page_rows, page_stride,
                page_tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance, sigmoid_weights, head_offset,
-               static_cast<const T*>(gate), gate_stride, gate_per_head);
+               static_cast<const T*>(gate), gate_stride, gate_per_head, splits, partial);
+    int status = tau_launch_status();
+    if (status != 0 || !partial) return status;
+    tau_launch(masked_attention_merge_kernel<T>, dim3(tokens, heads), dim3(128), 0, s, partial, static_cast<T*>(out), out_stride, heads, vdim, splits, out_scale,
+               sigmoid_weights, static_cast<const T*>(gate), gate_stride, gate_per_head);
     return tau_launch_status();
 }
 
+// out[r, c] = values[r, c] * sigmoid(gate[r, c]); rows of the three any distance apart, `out` may be `values`.
+template <typename T>
+__global__ void __launch_bounds__(256)
+sigmoid_gate_kernel(const T* __restrict__ values, long long values_stride, const T* __restrict__ gate, long long gate_stride, T* __restrict__ out,
+                    long long out_stride, int width) {
+    grid_dependents_launch();
+    grid_dependency_wait();
+    const size_t row = blockIdx.x;
+    for (int column = threadIdx.x; column < width; column += blockDim.x)
+        out[row * out_stride + column] = from_float<T>(to_float(values[row * values_stride + column]) / (1.0f + expf(-to_float(gate[row * gate_stride + column]))));
+}
+
 }  // namespace
+
+TAU_EXPORT int tau_sigmoid_gate(int dtype, const void* values, long long values_stride, const void* gate, long long gate_stride, void* out, long long out_stride,
+                                int rows, int width, void* stream) {
+    if (rows <= 0) return 0;
+    if (!values || !gate || !out || width <= 0) return cudaErrorInvalidValue;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == TAU_F32)
+        tau_launch(sigmoid_gate_kernel<float>, dim3(rows), dim3(256), 0, s, static_cast<const float*>(values), values_stride, static_cast<const float*>(gate), gate_stride,
+                   static_cast<float*>(out), out_stride, width);
+    else if (dtype == TAU_BF16)
+        tau_launch(sigmoid_gate_kernel<bf16>, dim3(rows), dim3(256), 0, s, static_cast<const bf16*>(values), values_stride, static_cast<const bf16*>(gate), gate_stride,
+                   static_cast<bf16*>(out), out_stride, width);
+    else return cudaErrorInvalidValue;
+    return tau_launch_status();
+}
 
 TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long projected_stride, const float* q_weight, const float* k_weight, float eps,
                                   const float* frequency, int rotary, float magnitude, void* queries, void* rows, void* value_pages, const int* positions,
@@ -431,7 +516,8 @@ TAU_EXPORT int tau_masked_prepare(int dtype, const void* projected, long long pr
 TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* rows, const void* value_pages, void* out, long long out_stride, const int* positions,
                                     const int* token_seq, const int* page_rows, int page_stride, int page_tokens, int tokens, int heads, int kv_heads,
                                     int dim, int vdim, float scale, int window, int chunk, int sink, float out_scale, int staged, const float* distance,
-                                    int sigmoid_weights, const float* head_offset, const void* gate, long long gate_stride, int gate_per_head, void* stream) {
+                                    int sigmoid_weights, const float* head_offset, const void* gate, long long gate_stride, int gate_per_head, int splits,
+                                    float* partial, void* stream) {
     if (tokens <= 0) return 0;
     if (!queries || !rows || !out || !positions || !token_seq || !page_rows || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || dim <= 0 ||
         vdim <= 0 || vdim > 32 * kMaxOwned || window < 0 || chunk < 0 || (window > 0 && chunk > 0) || (sigmoid_weights && sink))
@@ -444,10 +530,10 @@ TAU_EXPORT int tau_masked_attention(int dtype, const void* queries, const void* 
             if (dtype == TAU_F32)
                 return launch_staged<float>(staged_size, queries, rows, value_pages, out, out_stride, positions, token_seq, page_rows, page_stride, page_tokens,
                                             tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance, sigmoid_weights, head_offset, gate, gate_stride,
-                                            gate_per_head, s);
+                                            gate_per_head, splits, partial, s);
             return launch_staged<bf16>(staged_size, queries, rows, value_pages, out, out_stride, positions, token_seq, page_rows, page_stride, page_tokens,
                                        tokens, heads, kv_heads, dim, vdim, scale, window, chunk, sink, out_scale, distance, sigmoid_weights, head_offset, gate, gate_stride,
-                                       gate_per_head, s);
+                                       gate_per_head, splits, partial, s);
         }
     }
     const size_t bytes = static_cast<size_t>(kWarps) * dim * sizeof(float);

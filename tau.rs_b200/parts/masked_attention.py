@@ -120,6 +120,15 @@ class MaskedAttention(JoinableMixer):
         if spec.weights == "sigmoid":
             self.head_offset = held[f"{prefix}.pb"]
 
+    def _splits(self, step) -> int:
+        """Ranges that a step of single tokens cuts every context into: what the captured graph fixed, or chosen from the step; a window or
+        a chunk bounds what a token reads, and a range holds at least 64 positions."""
+        if not step.all_single:
+            return 1
+        splits = step.decode_splits or kernels.decode_splits(step.n_seqs, step.max_len, self.decode_blocks())
+        reach = self.spec.window or self.spec.chunk
+        return max(1, min(splits, -(-reach // 64))) if reach else splits
+
     def extra_cache_needs(self):
         if self.spec.taps > 1:
             return {"taps": CacheNeed("state", state_shape=(self.spec.taps - 1, self.conv_width), state_dtype=torch.float32)}
@@ -129,6 +138,11 @@ class MaskedAttention(JoinableMixer):
         if self.heads_layout:
             return CacheNeed("kv", n_kv_heads=self.spec.n_kv_heads, head_dim=self.spec.dim, window=self.spec.window, chunk=self.spec.chunk)
         return CacheNeed("rows", row_width=self.k_width + self.v_width, window=self.spec.window, chunk=self.spec.chunk)
+
+    def decode_blocks(self):
+        """Blocks of the staged kernel per sequence and context split: one per key/value head and pass over its query heads."""
+        group = self.spec.n_heads // self.spec.n_kv_heads
+        return self.spec.n_kv_heads * -(-group // kernels.MASKED_STAGED_WARPS)
 
     def mix(self, projected, gates, step, cache, writes_cache: bool, out) -> None:
         spec = self.spec
@@ -147,12 +161,15 @@ class MaskedAttention(JoinableMixer):
                                0 if position is None else spec.position.rotary_dim, 1.0 if position is None else position.magnitude, queries, keys,
                                step.positions, step.token_seq, pages, spec.n_heads, spec.n_kv_heads, spec.dim, spec.value_dim, writes_cache and spec.own_keys, values,
                                temperature=spec.temperature)
-        plain = spec.weights == "softmax" and not spec.distance_bias and gate is None
-        if (plain and self.heads_layout and not step.all_single and projected.dtype == torch.bfloat16 and kernels.optimized_preferred()
+        if (self.heads_layout and not step.all_single and projected.dtype == torch.bfloat16 and kernels.optimized_preferred()
                 and keys.shape[0] * spec.n_kv_heads * kernels.PAGE_TOKENS <= 0x7FFFFFFF and out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0):
+            # Runs of new tokens on the tensor cores; a gate per head leaves with the rows, a gate per element is a pass of its own.
             kernels.attention_prefill_tc(queries.view(tokens, -1), keys, values, out, step.cu_seqlens, step.seq_start, pages, spec.n_heads, spec.n_kv_heads,
-                                         spec.dim, spec.softmax_scale, spec.window or 0, spec.chunk or 0, spec.sink, self.out_scale)
+                                         spec.dim, spec.softmax_scale, spec.window or 0, spec.chunk or 0, spec.sink, self.out_scale, distance=self.distance,
+                                         sigmoid_weights=spec.weights == "sigmoid", head_offset=self.head_offset, head_gate=gate if spec.gate == "head" else None)
+            if spec.gate == "element":
+                kernels.gated_rows(out, gate, out)
             return
         kernels.masked_attention(queries, keys, out, step, pages, spec.n_kv_heads, spec.value_dim, spec.softmax_scale, spec.window or 0,
-                                 spec.chunk or 0, spec.sink, self.out_scale, values, staged=step.all_single, distance=self.distance,
+                                 spec.chunk or 0, spec.sink, self.out_scale, values, staged=step.all_single, splits=self._splits(step), distance=self.distance,
                                  sigmoid_weights=spec.weights == "sigmoid", head_offset=self.head_offset, gate=gate, gate_per_head=spec.gate == "head")

@@ -243,9 +243,10 @@ def test_the_delta_rule_with_a_decay_per_channel_carries_its_state(heads, key_he
 
 
 # ---- attention: sigmoid weights, the distance bias, gates, the temperature ---------------------------------------------
-def run_attention(kind_of, q, k, v, gate, dtype, page_of, heads_layout, extra, single_from):
+def run_attention(kind_of, q, k, v, gate, dtype, page_of, heads_layout, extra, single_from, tensor_cores=False):
     """The attention kernels over pages that lie scattered: positions up to `single_from` in one run, the rest one token to a step
-    (the staged kernel).  q [tokens, heads, dim], k/v [tokens, kv_heads, dim or vdim] as the prepare kernel would have left them."""
+    (the staged kernel, the context cut into 1, 2, 3, ... ranges in turn).  q [tokens, heads, dim], k/v [tokens, kv_heads, dim or vdim] as
+    the prepare kernel would have left them.  `tensor_cores`: the run goes through the tcgen05 kernel (pages of heads, bfloat16)."""
     kind = TORCH[dtype]
     tokens, heads, dim = q.shape
     kv_heads, vdim = k.shape[1], v.shape[2]
@@ -265,8 +266,17 @@ def run_attention(kind_of, q, k, v, gate, dtype, page_of, heads_layout, extra, s
     out = torch.empty((tokens, heads * vdim), dtype=kind, device=DEVICE)
     for begin, end, staged in [(0, single_from, False)] + [(position, position + 1, True) for position in range(single_from, tokens)]:
         step = SimpleNamespace(positions=as_ints(list(range(begin, end))), token_seq=as_ints([0] * (end - begin)))
+        gate_rows = None if gate is None else on_device(gate[begin:end], kind)
+        if tensor_cores and not staged:
+            per_head = kind_of.get("gate") == "head"
+            kernels.attention_prefill_tc(on_device(q[begin:end], kind).view(end - begin, -1), rows, values, out[begin:end], as_ints([0, end - begin]), as_ints([begin]), pages,
+                                         heads, kv_heads, dim, kind_of["scale"], 0, distance=extra.get("distance"), sigmoid_weights=extra.get("sigmoid_weights", False),
+                                         head_offset=extra.get("head_offset"), head_gate=gate_rows if per_head else None)
+            if gate_rows is not None and not per_head:
+                kernels.gated_rows(out[begin:end], gate_rows, out[begin:end])
+            continue
         kernels.masked_attention(on_device(q[begin:end], kind), rows, out[begin:end], step, pages, kv_heads, vdim, kind_of["scale"], value_pages=values, staged=staged,
-                                 gate=None if gate is None else on_device(gate[begin:end], kind), gate_per_head=kind_of.get("gate") == "head", **extra)
+                                 gate=gate_rows, gate_per_head=kind_of.get("gate") == "head", splits=1 + (begin - single_from) % 5 if staged else 1, **extra)
     return out.float().cpu()
 
 
@@ -293,6 +303,15 @@ def test_sigmoid_weights_and_distance_biased_softmax_over_scattered_pages(dtype,
     found = run_attention({"scale": dim ** -0.5, "gate": "element"}, q, k, v, gate, dtype, page_of, heads_layout,
                           dict(distance=on_device(torch.stack([r1, r2], dim=1))), single_from=140)
     assert relative_error(found, wanted) < tolerance
+    if heads_layout and dtype == "bfloat16":        # the same runs on the tensor cores
+        found = run_attention({"scale": dim ** -0.5, "gate": "element"}, q, k, v, gate, dtype, page_of, True, dict(distance=on_device(torch.stack([r1, r2], dim=1))),
+                              single_from=140, tensor_cores=True)
+        assert relative_error(found, wanted) < tolerance
+        gate = rounded(rand(generator, tokens, heads))
+        wanted = plain.sigmoid_attention(q, k, v, dim ** -0.5, offset) * torch.sigmoid(gate)[:, :, None]
+        found = run_attention({"scale": dim ** -0.5, "gate": "head"}, q, k, v, gate, dtype, page_of, True, dict(sigmoid_weights=True, head_offset=on_device(offset)),
+                              single_from=140, tensor_cores=True)
+        assert relative_error(found, wanted.reshape(tokens, -1)) < tolerance
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
