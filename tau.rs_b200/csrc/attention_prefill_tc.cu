@@ -15,7 +15,7 @@
 // A second form of the kernel (`kExtended`, chosen by the launcher where a caller asks for any of this) serves other weights: a bias that
 // falls with the logarithm of the distance, `- r1 log(1 + r2 (i - j))` with two numbers per head, enters the scores before the maximum
 // (in the exponent's base-2 scale, one `lg2.approx` a score); sigmoid weights `sigmoid(score + offset[head])` replace the softmax (no
-// maximum, no sum, no rescaling: every probability stands alone); and a gate per (token, head) multiplies the row as it leaves.
+// maximum, no sum, no rescaling: every probability stands alone, one `tanh.approx` each); and a gate per (token, head) multiplies the row as it leaves.
 //
 // The accumulator O is rescaled only when a row's maximum has grown by more than 2^8 since the last rescale, so most
 // tiles do not touch it; the final division by the row sum makes the result exact either way.  The score products run
@@ -205,6 +205,12 @@ __device__ __forceinline__ float fast_exp2(float value) {
     return result;
 }
 
+__device__ __forceinline__ float fast_tanh(float value) {
+    float result;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(result) : "f"(value));
+    return result;
+}
+
 // Two 32-bit floats in one 64-bit register for the packed arithmetic of sm_100 (one instruction, two results): the softmax
 // warps are bound by the instructions they issue, and half of a row's scalings and sums are instructions saved.
 typedef unsigned long long Float2;
@@ -246,6 +252,7 @@ struct Item {
 };
 
 struct Shared {
+    float bias[4][96];              // per softmax warp: the distance bias of a tile's 32 rows and 64 keys by distance (95 values)
     uint64_t q_full;                // the Q tile of an item has landed
     uint64_t q_free;                // the last scores of an item are done: the place of its Q tile may be written
     uint64_t k_full[kKeyStages];    // a key tile has landed
@@ -600,12 +607,20 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 const bool all_seen = key0 + BN - 1 <= warp_first && (!bounded || key0 >= first_seen(warp_last, window, chunk));
                 const bool none_seen = key0 > warp_last || (bounded && key0 + BN - 1 < first_seen(warp_first, window, chunk));
                 if (biased && !none_seen) {
-                    // score * scale * log2(e) - r1 * log2(1 + r2 * distance); keys behind the query (masked below) count as distance 0.
+                    // score * scale * log2(e) - r1 * log2(1 + r2 * distance).  The warp's 32 rows and the tile's 64 keys lie 95 different
+                    // distances apart: the lanes compute the bias once for each (three to a lane) and every row reads its 64 from
+                    // shared memory, neighbouring lanes neighbouring words.  Keys behind the query (masked below) count as distance 0.
+                    float* table = shared->bias[warp];
+                    __syncwarp();      // the table of the tile before has been read
+                    const int nearest = warp_first - key0 - (BN - 1);      // the distance of the warp's first row from the tile's last key
 #pragma unroll
-                    for (int j = 0; j < BN; ++j) {
-                        const int apart = position - key0 - j;
-                        score[j] = fmaf(score[j], scale_log2, -far * __log2f(fmaf(reach, static_cast<float>(apart > 0 ? apart : 0), 1.0f)));
+                    for (int entry = lane; entry < 32 + BN - 1; entry += 32) {
+                        const int apart = nearest + entry;
+                        table[entry] = far * __log2f(fmaf(reach, static_cast<float>(apart > 0 ? apart : 0), 1.0f));
                     }
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < BN; ++j) score[j] = fmaf(score[j], scale_log2, -table[lane + (BN - 1) - j]);
                 }
                 if (!all_seen && !none_seen) {
                     const int highest = position - key0;
@@ -677,8 +692,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     tensor_store_words_16(lane_base + (tile & 1) * BN + 16, zeros);
                 } else {
                     Float2 partial_sum[4] = {pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f), pair_of(0.0f, 0.0f)};
-                    // Sigmoid weights: 1 / (1 + 2^-(score + offset)) with both in the base-2 scale; a masked score of -inf gives 1 / inf = 0.
-                    const float added = sigmoid ? -offset_log2 : -subtract, factor = sigmoid ? -tile_scale : tile_scale;
+                    // Sigmoid weights: sigmoid(x) = 0.5 tanh(x / 2) + 0.5 with x = score * scale + offset, one special-function instruction a
+                    // weight (`tanh.approx`, within 2^-10 of the weight, which is then rounded to bfloat16); a masked score of -inf gives 0.
+                    constexpr float kHalfLn2 = 0.34657359027997264f;      // the scale and the offset arrive in the base-2 scale
+                    const float added = sigmoid ? offset_log2 * kHalfLn2 : -subtract, factor = sigmoid ? tile_scale * kHalfLn2 : tile_scale;
                     const Float2 scale_pair = pair_of(factor, factor), shift_pair = pair_of(added, added);
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {   // 32 keys are 16 columns
@@ -687,8 +704,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                         for (int j = 0; j < 32; j += 2) {
                             float x0, x1;
                             unpair(fma_pair(pair_of(score[half * 32 + j], score[half * 32 + j + 1]), scale_pair, shift_pair), x0, x1);
-                            float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-                            if (sigmoid) p0 = __frcp_rn(1.0f + p0), p1 = __frcp_rn(1.0f + p1);
+                            float p0, p1;
+                            if (sigmoid) p0 = fmaf(fast_tanh(x0), 0.5f, 0.5f), p1 = fmaf(fast_tanh(x1), 0.5f, 0.5f);
+                            else p0 = fast_exp2(x0), p1 = fast_exp2(x1);
                             partial_sum[(j >> 1) & 3] = add_pair(partial_sum[(j >> 1) & 3], pair_of(p0, p1));
                             packed[j / 2] = pack_bf16(p0, p1);
                         }
