@@ -350,12 +350,12 @@ def nugolorn_sizes():
     def nugolorn(width, heads, expert_ff):
         sigmoid = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "conv": 4, "rot": {"base": 10000.0, "dims": 64}}
         memory = {"heads": width // 64, "dim": 64, "decay_rank": 64}
-        left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.3, "every": 512}}
+        left = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "q_temp": {"coef": 0.25, "every": 512}}
         right = {"heads": heads, "kv_heads": heads // 2, "dim": 128, "vdim": 128, "conv": 4, "decay_rank": 64, "gate_rank": 64}
         dense, routed = {"kind": "dense", "ff": 4 * width}, {"kind": "moe", "router": {"experts": 32, "identity": 4, "top": 4}, "expert": {"ff": expert_ff}}
         layers = [{"type": "attention", "mixer": sigmoid, "mlp": dense}, {"type": "wkv", "mixer": memory, "mlp": routed},
                   {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": dense}, {"type": "attention", "mixer": dict(sigmoid, kv_from=0), "mlp": routed}]
-        return {"architecture": "Nugolorn", "layers": layers, "norm": {"eps": 1e-5, "groups": 4}, "residual_mult": 0.7, "logit_scale": 0.25, "vocab": 32768, "width": width}
+        return {"architecture": "Nugolorn", "layers": layers, "norm": {"eps": 1e-5, "groups": 8}, "residual_mult": 0.8, "logit_scale": 0.5, "vocab": 32768, "width": width}
 
     pegurax = pegurax_sizes()
     return {
