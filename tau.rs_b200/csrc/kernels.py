@@ -208,7 +208,7 @@ def add_rms_norm(branch, residual, weight, eps: float, out, groups: int = 1, bra
            "add_rms_norm")
 
 
-NORM_MAX_GROUPS = 64
+NORM_MAX_GROUPS = 1024
 
 
 def stream_add_norm(stream, branches, weight, eps: float, out, rows=None, update: bool = True, groups: int = 1, branch_scale: float = 1.0) -> None:

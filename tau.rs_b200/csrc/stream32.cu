@@ -26,7 +26,7 @@ __global__ void embedding_f32_kernel(const int* __restrict__ tokens, const T* __
 // r = rows ? rows[i] : i.  sum = stream[r] + branch_scale * (a[r] + b[r]) in 32-bit; if `update` the sum replaces stream[r];
 // out[i] = sum / sqrt(mean(sum^2) + eps) * weight, rounded once to T.  With `groups` > 1 the row is cut into that many equal
 // consecutive pieces and each is divided by its own root mean square (a warp sums a piece's squares).
-constexpr int kMaxNormGroups = 64;
+constexpr int kMaxNormGroups = 1024;
 
 template <typename T>
 __global__ void __launch_bounds__(kThreads)

@@ -121,13 +121,13 @@ class MaskedAttention(JoinableMixer):
             self.head_offset = held[f"{prefix}.pb"]
 
     def _splits(self, step) -> int:
-        """Ranges that a step of single tokens cuts every context into: what the captured graph fixed, or chosen from the step; a window or
-        a chunk bounds what a token reads, and a range holds at least 64 positions."""
+        """Ranges that a step of single tokens cuts every context into: as many as fill the machine with the staged kernel's blocks (six
+        to an SM), each at least 64 positions of what a token reads (its window or chunk bounds that), 32 at most.  Any number computes
+        the same sums, so a captured graph that serves other lengths than the one it was captured at stays right."""
         if not step.all_single:
             return 1
-        splits = step.decode_splits or kernels.decode_splits(step.n_seqs, step.max_len, self.decode_blocks())
-        reach = self.spec.window or self.spec.chunk
-        return max(1, min(splits, -(-reach // 64))) if reach else splits
+        reach = min(step.max_len, self.spec.window or self.spec.chunk or step.max_len)
+        return max(1, min(6 * kernels.sm_count() // max(1, step.n_seqs * self.decode_blocks()), reach // 64, 32))
 
     def extra_cache_needs(self):
         if self.spec.taps > 1:
