@@ -9,8 +9,8 @@
 //            last input for a run's first token, zeros when the sequence starts): mix_s = h + (h' - h) * mu_s, for `mixes` vectors mu.
 //   decay:   in place, w = exp(-exp(x + w0)) per head and key channel; and tanh in place for the low-rank step before it.
 //   walk:    one block owns (sequence, head, tile of value columns) and walks the run's tokens in order, the next tokens' r, k, w and
-//            values on their way into a ring in shared memory meanwhile (cp.async).  A column of S is shared by kSplit threads with
-//            kRows key rows each in registers; a token costs one pass over the rows and one barrier.
+//            values on their way into shared memory meanwhile (cp.async).  A column of S is shared by kSplit threads with kRows key
+//            rows each in registers; a token costs one pass over the rows, and the threads of a column meet once in four tokens (two for very wide keys).
 //
 // The state is 32-bit and lives in the cache, [heads, value_dim, key_dim] per slot.  TAU_KEY_DIM fixes key_dim.
 #include "common.cuh"
@@ -22,10 +22,11 @@
 namespace {
 
 constexpr int kDim = TAU_KEY_DIM;
-constexpr int kSplit = kDim <= 16 ? 1 : kDim <= 32 ? 2 : kDim <= 64 ? 4 : kDim <= 128 ? 8 : kDim <= 256 ? 16 : 32;   // threads that share a column
+// Threads that share a column: four key rows to a thread where the width allows, so that a token's chain of dependent instructions is
+// short and a scheduler has warps to choose from even when a prompt brings one block to an SM.
+constexpr int kSplit = kDim <= 4 ? 1 : kDim <= 8 ? 2 : kDim <= 16 ? 4 : kDim <= 32 ? 8 : kDim <= 64 ? 16 : 32;
 constexpr int kRows = (kDim + kSplit - 1) / kSplit;
 constexpr bool kExact = kDim % kSplit == 0;
-constexpr int kRing = kDim <= 256 ? 8 : 4;
 constexpr int kThreads = 256;
 
 // grid (tokens, blocks of columns).  x [tokens, width]; last [slots, width] float: each sequence's last input.  mu [mixes, width];
@@ -81,6 +82,13 @@ __device__ __forceinline__ void copy_commit() { asm volatile("cp.async.commit_gr
 template <int N> __device__ __forceinline__ void copy_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // r, k, w [tokens, heads * kDim], v [tokens, heads * value_dim], bonus [heads, kDim], all float; out [tokens, heads * value_dim] float.
+// A thread's rows of S depend on nobody else's, so the walk takes kGroup tokens between two barriers: the threads that share a column
+// meet only to add up their parts of the read-outs, once per group, and a group's r, k, w and values arrive as one set of copies while
+// the groups before are walked (kDepth groups in the ring: a set of copies has kDepth - 1 groups' time to arrive).
+constexpr int kGroup = kDim <= 256 ? 4 : 2;      // (two for very wide keys: the ring stays within the static shared memory)
+
+constexpr int kDepth = kDim <= 64 ? 4 : kDim <= 128 ? 3 : 2;
+
 template <int kColumns>
 __global__ void __launch_bounds__(kColumns * kSplit)
 wkv_kernel(const float* __restrict__ r, const float* __restrict__ k, const float* __restrict__ v, const float* __restrict__ w, const float* __restrict__ bonus,
@@ -88,8 +96,8 @@ wkv_kernel(const float* __restrict__ r, const float* __restrict__ k, const float
            int heads, int value_dim) {
     grid_dependents_launch();
     grid_dependency_wait();
-    __shared__ __align__(16) float rs[kRing][kDim], ks[kRing][kDim], ws[kRing][kDim];
-    __shared__ float vs[kRing][kColumns], parts[2][kSplit][kColumns];
+    __shared__ __align__(16) float rs[kDepth][kGroup][kDim], ks[kDepth][kGroup][kDim], ws[kDepth][kGroup][kDim];
+    __shared__ float vs[kDepth][kGroup][kColumns], parts[kGroup][kSplit][kColumns];
     const int head = blockIdx.x, sequence = blockIdx.y;
     const int local = threadIdx.x % kColumns, part = threadIdx.x / kColumns, row0 = part * kRows;
     const int column = blockIdx.z * kColumns + local;
@@ -102,51 +110,66 @@ wkv_kernel(const float* __restrict__ r, const float* __restrict__ k, const float
         own[i] = row0 + i < kDim ? bonus[static_cast<size_t>(head) * kDim + row0 + i] : 0.0f;
     }
     const int begin = cu_seqlens[sequence], end = cu_seqlens[sequence + 1];
+    const int groups = (end - begin + kGroup - 1) / kGroup;
     constexpr int kStage = (kDim + kColumns * kSplit - 1) / (kColumns * kSplit);
-    // One group of copies per token, empty ones too, so that the count of groups in flight says which tokens have arrived.
-    auto stage = [&](int index) {
-        const int token = begin + index, place = index % kRing;
-        if (token < end) {
-            const size_t keys = (static_cast<size_t>(token) * heads + head) * kDim;
+    // One set of copies per group of tokens, empty ones too, so that the count of sets in flight says which groups have arrived.
+    auto stage = [&](int group) {
+        const int half = group % kDepth;
 #pragma unroll
-            for (int i = 0; i < kStage; ++i) {
-                const int d = threadIdx.x + i * kColumns * kSplit;
-                if (d < kDim) {
-                    copy_float(&rs[place][d], r + keys + d);
-                    copy_float(&ks[place][d], k + keys + d);
-                    copy_float(&ws[place][d], w + keys + d);
+        for (int t = 0; t < kGroup; ++t) {
+            const int token = begin + group * kGroup + t;
+            if (group < groups && token < end) {
+                const size_t keys = (static_cast<size_t>(token) * heads + head) * kDim;
+#pragma unroll
+                for (int i = 0; i < kStage; ++i) {
+                    const int d = threadIdx.x + i * kColumns * kSplit;
+                    if (d < kDim) {
+                        copy_float(&rs[half][t][d], r + keys + d);
+                        copy_float(&ks[half][t][d], k + keys + d);
+                        copy_float(&ws[half][t][d], w + keys + d);
+                    }
                 }
+                if (part == 0 && live) copy_float(&vs[half][t][local], v + (static_cast<size_t>(token) * heads + head) * value_dim + column);
             }
-            if (part == 0 && live) copy_float(&vs[place][local], v + (static_cast<size_t>(token) * heads + head) * value_dim + column);
         }
         copy_commit();
     };
 #pragma unroll
-    for (int index = 0; index < kRing - 1; ++index) stage(index);
-    copy_wait<kRing - 2>();
-    __syncthreads();
-    for (int token = begin; token < end; ++token) {
-        const int index = token - begin, place = index % kRing, half = index & 1;
-        const float value = live ? vs[place][local] : 0.0f;
-        float sums[2] = {0.0f, 0.0f};
+    for (int group = 0; group < kDepth; ++group) stage(group);
+    for (int group = 0; group < groups; ++group) {
+        const int half = group % kDepth, first = begin + group * kGroup;
+        const int count = end - first < kGroup ? end - first : kGroup;
+        copy_wait<kDepth - 1>();      // this thread's copies of the group are done (those of the next groups may be on their way)
+        __syncthreads();     // everybody's are; and the parts of the group before have been added up
+        // A whole group is walked without a branch, so that the loads of all its tokens can be on their way at once.
+        auto walk = [&](int t) {
+            const float value = live ? vs[half][t][local] : 0.0f;
+            float sums[2] = {0.0f, 0.0f};
 #pragma unroll
-        for (int i = 0; i < kRows; ++i) {
-            if (kExact || row0 + i < kDim) {
-                const float write = ks[place][row0 + i] * value;                       // the token's own k v^T, this thread's rows of this column
-                sums[i & 1] = fmaf(fmaf(own[i], write, S[i]), rs[place][row0 + i], sums[i & 1]);
-                S[i] = fmaf(ws[place][row0 + i], S[i], write);
+            for (int i = 0; i < kRows; ++i) {
+                if (kExact || row0 + i < kDim) {
+                    const float write = ks[half][t][row0 + i] * value;                 // the token's own k v^T, this thread's rows of this column
+                    sums[i & 1] = fmaf(fmaf(own[i], write, S[i]), rs[half][t][row0 + i], sums[i & 1]);
+                    S[i] = fmaf(ws[half][t][row0 + i], S[i], write);
+                }
             }
-        }
-        parts[half][part][local] = sums[0] + sums[1];
-        // The place of the token before this one is free: everybody has passed that token's barrier, and read its place before it.
-        stage(index + kRing - 1);
-        copy_wait<kRing - 2>();
-        __syncthreads();
-        if (part == 0 && live) {
-            float sum = 0.0f;
+            parts[t][part][local] = sums[0] + sums[1];
+        };
+        if (count == kGroup) {
 #pragma unroll
-            for (int p = 0; p < kSplit; ++p) sum += parts[half][p][local];
-            out[(static_cast<size_t>(token) * heads + head) * value_dim + column] = sum;
+            for (int t = 0; t < kGroup; ++t) walk(t);
+        } else {
+            for (int t = 0; t < count; ++t) walk(t);
+        }
+        __syncthreads();     // the parts are complete, and the group's place in the ring may be written over
+        stage(group + kDepth);
+        if (live) {      // the threads of a column share the group's tokens among them
+            for (int t = part; t < count; t += kSplit) {
+                float sum = 0.0f;
+#pragma unroll
+                for (int p = 0; p < kSplit; ++p) sum += parts[t][p][local];
+                out[(static_cast<size_t>(first + t) * heads + head) * value_dim + column] = sum;
+            }
         }
     }
     copy_wait<0>();
@@ -211,10 +234,15 @@ TAU_EXPORT int tau_wkv(const float* r, const float* k, const float* v, const flo
     if (n_seqs <= 0) return 0;
     if (!r || !k || !v || !w || !bonus || !state || !cu_seqlens || !seq_slot || !out || heads <= 0 || value_dim <= 0) return cudaErrorInvalidValue;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool narrow = heads * n_seqs * ((value_dim + 31) / 32) < 148 && kSplit <= 16;     // blocks of 16 columns reach more SMs
-    const int tile = narrow ? 16 : 32;
+    // Value columns to a block: 32 where that many blocks fill the machine, else 16 (blocks of 8 and 4 columns were slower: every block
+    // brings the head's r, k and w for itself, and that, not the walk, is then a block's work).
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+    const int tile = static_cast<long long>(heads) * n_seqs * ((value_dim + 31) / 32) < sms ? 16 : 32;
     dim3 grid(heads, n_seqs, (value_dim + tile - 1) / tile), block(tile * kSplit);
-    if (narrow) tau_launch(wkv_kernel<16>, grid, block, 0, s, r, k, v, w, bonus, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim);
-    else tau_launch(wkv_kernel<32>, grid, block, 0, s, r, k, v, w, bonus, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim);
+#define TAU_WKV(COLUMNS) tau_launch(wkv_kernel<COLUMNS>, grid, block, 0, s, r, k, v, w, bonus, state, slot_stride, cu_seqlens, seq_slot, out, heads, value_dim)
+    if (tile == 32) TAU_WKV(32);
+    else TAU_WKV(16);
+#undef TAU_WKV
     return tau_launch_status();
 }
