@@ -50,6 +50,8 @@ class RoutedExperts(FeedForward):
         self.identity = getattr(spec, "identity", 0)
         if self.identity < 0:
             raise ValueError("the number of identity experts cannot be negative")
+        if self.identity and getattr(spec, "weigh", "output") == "input":
+            raise ValueError("identity experts are summed with their weights on the output; weights on the experts' input are not served beside them")
         self.outputs = spec.experts + self.identity      # what the router scores
         if spec.top > self.outputs:
             raise ValueError("top must lie between 1 and the number of router outputs")
